@@ -2,7 +2,8 @@
 
 A mixer states what it needs per sequence: keys and values for all positions
 (`KVRequest(window=None)`), for a window of them (`window=W`), a state of fixed
-size (`StateRequest`), or nothing. Cache entries with the same key-value shape
+size (`StateRequest`), both at once (`JointRequest`: a mixer made of an attention
+and a recurrence side by side), or nothing. Cache entries with the same key-value shape
 and policy form a group with storage and a page pool of its own:
 
     storage[entry, page, 0 = keys / 1 = values, kv head, row in page, head_dim]
@@ -41,7 +42,14 @@ class StateRequest:
     dtype: torch.dtype = torch.float32
 
 
-CacheRequest = Union[KVRequest, StateRequest, None]
+@dataclass(frozen=True)
+class JointRequest:
+    """Keys and values AND a state row for the same cache entry."""
+    kv: KVRequest
+    state: StateRequest
+
+
+CacheRequest = Union[KVRequest, StateRequest, JointRequest, None]
 
 
 class KVGroup:
@@ -120,6 +128,13 @@ class StateView:
     writes: bool
 
 
+@dataclass
+class JointView:
+    """What a mixer that asked for both sees: its pages and its state rows."""
+    kv: KVView
+    state: StateView
+
+
 class SequenceCache:
     """All cache memory of an engine: groups, state, and the slot table."""
 
@@ -135,6 +150,9 @@ class SequenceCache:
         self.state: Dict[int, torch.Tensor] = {}
         for entry in sorted(requests):
             req = requests[entry]
+            if isinstance(req, JointRequest):  # the entry is in a page group and has state rows
+                by_key.setdefault(req.kv, []).append(entry)
+                req = req.state
             if isinstance(req, KVRequest):
                 by_key.setdefault(req, []).append(entry)
             elif isinstance(req, StateRequest):
@@ -202,6 +220,9 @@ class SequenceCache:
 
     # --------------------------------------------------------------- views
     def view(self, entry: int, writes: bool):
+        if entry in self.group_of and entry in self.state:
+            return JointView(KVView(self.group_of[entry], entry, writes),
+                             StateView(self.state[entry], entry, writes))
         if entry in self.group_of:
             return KVView(self.group_of[entry], entry, writes)
         if entry in self.state:

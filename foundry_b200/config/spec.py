@@ -83,6 +83,7 @@ class ModelSpec:
     embedding: Optional[PartSpec] = None  # None: the plain table lookup
     junctions: Tuple[PartSpec, ...] = ()
     junction_prefixes: Tuple[str, ...] = ()  # tensor-name prefix of each junction
+    logit_softcap: Optional[float] = None  # c: logits <- c * tanh(logits / c)
 
     def cache_entry_count(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)

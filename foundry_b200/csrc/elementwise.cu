@@ -441,3 +441,24 @@ FB_API int fb_sum_planes(const float* planes, int S, long long n, long long plan
                                        planes, S, n, plane_stride, (TO*)out)));
   return fb_check_launch("sum_planes");
 }
+
+// ------------------------------------------------------------- cap on values
+// x <- cap * tanh(x / cap), in place, 32-bit (a soft cap on the logits).
+namespace {
+__global__ void softcap_kernel(float* x, long long n, float cap) {
+  fb_pdl_wait();
+  const float inv = 1.0f / cap;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv);
+}
+}  // namespace
+
+FB_API int fb_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+  FB_REQUIRE(n >= 0 && cap > 0.f, "softcap: bad arguments n=%lld cap=%f", n, (double)cap);
+  if (n == 0) return 0;
+  const long long want = (n + 255) / 256;
+  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  fb_launch(softcap_kernel, dim3(blocks), dim3(256), 0, stream, x, n, cap);
+  return fb_check_launch("softcap");
+}

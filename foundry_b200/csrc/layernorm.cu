@@ -13,15 +13,51 @@
 // (the first norm of a model has no y, the last sum no h). Statistics, the sum
 // and the residual are 32-bit; the variance is the mean of squared deviations
 // taken in a second pass over the row held in shared memory.
+//
+// Between the two halves the stream may be replaced by a weighted sum over the
+// streams that the layers so far have left (a depth-wise average):
+//
+//   X_n = resid (after the sum);   resid <- sum_j mix[j] X_j,  j = 0 .. n
+//
+// X_0 is `first` (the stream as the embedding left it), X_1 .. X_n are the rows
+// of `kept` ([n, T, W]; X_n is written here), and the terms are added in the
+// order of j.
 #include "common.cuh"
 
 namespace {
+
+struct DepthMix {
+  const float* first;    // X_0 [T, W]
+  float* kept;           // X_1 .. X_n, [n, T, W]
+  const float* weights;  // [n + 1] on the device
+  int n;                 // 0: no mixing
+  long long plane;       // T * W
+};
+
+// row[] holds the residual row after its sum; keeps it as X_n and replaces it (in
+// shared memory and in `x`) by the weighted sum over X_0 .. X_n.
+__device__ __forceinline__ void depth_mix_row(const DepthMix& m, float* row, float* x, size_t base,
+                                              int W) {
+  __syncthreads();
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float last = row[i];
+    m.kept[(size_t)(m.n - 1) * m.plane + base + i] = last;
+    float v = m.weights[0] * __ldcg(m.first + base + i);
+    for (int j = 1; j < m.n; ++j)
+      v = fmaf(m.weights[j], __ldcg(m.kept + (size_t)(j - 1) * m.plane + base + i), v);
+    v = fmaf(m.weights[m.n], last, v);
+    x[i] = v;
+    row[i] = v;
+  }
+  __syncthreads();
+}
 
 template <typename TY, typename TO>
 __global__ void ln_add_ln_kernel(const TY* y, const float* __restrict__ w1,
                                  const float* __restrict__ b1, float* resid,
                                  const float* __restrict__ w2, const float* __restrict__ b2,
-                                 TO* __restrict__ out, int W, float eps, float inv_w) {
+                                 TO* __restrict__ out, int W, float eps, float inv_w,
+                                 DepthMix mix) {
   fb_pdl_launch();
   fb_pdl_wait();
   extern __shared__ float row[];  // W floats
@@ -55,9 +91,10 @@ __global__ void ln_add_ln_kernel(const TY* y, const float* __restrict__ w1,
       x[i] = v;
       row[i] = v;
     }
-  } else if (out != nullptr) {
+  } else if (out != nullptr || mix.n > 0) {
     for (int i = threadIdx.x; i < W; i += blockDim.x) row[i] = x[i];
   }
+  if (mix.n > 0) depth_mix_row(mix, row, x, base, W);
   if (out == nullptr) return;
   float s = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];
@@ -106,7 +143,8 @@ template <typename TY, typename TO>
 __global__ void ln_add_ln_vec_kernel(const TY* y, const float* __restrict__ w1,
                                      const float* __restrict__ b1, float* resid,
                                      const float* __restrict__ w2, const float* __restrict__ b2,
-                                     TO* __restrict__ out, int W, float eps, float inv_w) {
+                                     TO* __restrict__ out, int W, float eps, float inv_w,
+                                     DepthMix mix) {
   fb_pdl_launch();
   fb_pdl_wait();
   extern __shared__ __align__(16) float row[];  // W floats
@@ -145,9 +183,10 @@ __global__ void ln_add_ln_vec_kernel(const TY* y, const float* __restrict__ w1,
       st4<float>(x + 4 * i, o);
       row4[i] = o;
     }
-  } else if (out != nullptr) {
+  } else if (out != nullptr || mix.n > 0) {
     for (int i = threadIdx.x; i < n4; i += blockDim.x) row4[i] = ld4<float>(x + 4 * i);
   }
+  if (mix.n > 0) depth_mix_row(mix, row, x, base, W);
   if (out == nullptr) return;
   float s = 0.f;
   for (int i = threadIdx.x; i < n4; i += blockDim.x) {
@@ -220,14 +259,18 @@ __global__ void add_row_vector_kernel(float* x, const float* __restrict__ v, int
 
 FB_API int fb_ln_add_ln(const void* y, int y_dtype, const float* w1, const float* b1, float* resid,
                         const float* w2, const float* b2, void* out, int out_dtype, int T, int W,
-                        float eps, cudaStream_t stream) {
+                        float eps, const float* mix_first, float* mix_kept,
+                        const float* mix_weights, int mix_n, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && W > 0 && eps > 0.f, "ln_add_ln: bad sizes T=%d W=%d", T, W);
   FB_REQUIRE(resid != nullptr, "ln_add_ln: no residual rows");
   FB_REQUIRE(y == nullptr || ((w1 != nullptr) == (b1 != nullptr)),
              "ln_add_ln: the norm of y has a weight or a bias but not both");
   FB_REQUIRE(out == nullptr || (w2 && b2), "ln_add_ln: the norm of the sum has no weight or bias");
   FB_REQUIRE((size_t)W * 4 <= 200 * 1024, "ln_add_ln: rows of %d do not fit shared memory", W);
-  if (T == 0 || (y == nullptr && out == nullptr)) return 0;
+  FB_REQUIRE(mix_n >= 0 && (mix_n == 0 || (mix_first && mix_kept && mix_weights)),
+             "ln_add_ln: a depth-wise average of %d kept streams lacks an input", mix_n);
+  if (T == 0 || (y == nullptr && out == nullptr && mix_n == 0)) return 0;
+  const DepthMix mix{mix_first, mix_kept, mix_weights, mix_n, (long long)T * W};
   const size_t smem = (size_t)W * 4;
   const bool vec = W % 4 == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)resid % 16) == 0 &&
                    ((uintptr_t)out % 16) == 0 && ((uintptr_t)w1 % 16) == 0 &&
@@ -247,10 +290,10 @@ FB_API int fb_ln_add_ln(const void* y, int y_dtype, const float* w1, const float
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
     if (vec)                                                                                   \
       fb_launch(ln_add_ln_vec_kernel<TY, TO>, dim3(T), dim3(threads), smem, stream,            \
-                (const TY*)y, w1, b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W);       \
+                (const TY*)y, w1, b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W, mix);  \
     else                                                                                       \
       fb_launch(ln_add_ln_kernel<TY, TO>, dim3(T), dim3(threads), smem, stream, (const TY*)y,  \
-                w1, b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W);                     \
+                w1, b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W, mix);                \
   } while (0)
   const int yd = y ? y_dtype : FB_F32, od = out ? out_dtype : FB_F32;
   FB_DISPATCH_DTYPE(yd, TY, FB_DISPATCH_DTYPE(od, TO, FB_LN_LAUNCH(TY, TO)));

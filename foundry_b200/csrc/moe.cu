@@ -1,13 +1,18 @@
 // A feed-forward of routed experts.
 //
-//   z = W_router h + b (32-bit);  the `top` experts of largest z are chosen
-//   (the lower index among equals);  their weights are softmax over the chosen
-//   z only;  y = sum_c weight_c * expert_c(h)
+//   z = W_router h (+ b) (32-bit). Two scoring rules (`score`):
+//   0: the `top` experts of largest z are chosen (the lower index among equals);
+//      their weights are the softmax over the chosen z only
+//   1: s = sigmoid(z); the experts form `groups` equal groups of neighbours, a group's
+//      score is the sum of its two largest s, only experts of the `keep` best groups can
+//      be chosen (groups 1: all); the `top` largest s are chosen and weighted by s itself
+//   y = sum_c weight_c * expert_c(h)
 //   expert:  g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit)
-//            a = g * sigmoid(alpha g) * (u + 1);  out = W_down a
+//            a = g * sigmoid(alpha g) * (u + shift);  out = W_down a
+//   (limit = infinity, alpha = 1, shift = 0: silu(g) * u)
 //
 // The experts' matrices are stacked: gate_up [E, 2 ff, W] (gate rows, then up
-// rows) and down [E, W, ff]. `limit`, `alpha` and the counts are parameters.
+// rows) and down [E, W, ff]. `limit`, `alpha`, `shift` and the counts are parameters.
 //
 // `fb_moe_route` makes the choice per token. `fb_moe_experts_rows` is the form
 // for a handful of tokens: one block per token streams the weights of that
@@ -19,17 +24,61 @@ namespace {
 
 __global__ void moe_route_kernel(const float* z, long long ld, const float* __restrict__ bias,
                                  int E, int top, int* __restrict__ chosen,
-                                 float* __restrict__ weights) {
+                                 float* __restrict__ weights, int score, int groups, int keep) {
   fb_pdl_launch();
   fb_pdl_wait();
   // one warp per token; each lane keeps the experts lane, lane + 32, ... (up to 8 of them)
+  __shared__ float s_all[256];
+  __shared__ float s_group[256];
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31;
   float v[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int e = lane + 32 * i;
-    v[i] = e < E ? __ldcg(z + (size_t)t * ld + e) + bias[e] : -INFINITY;
+    v[i] = -INFINITY;
+    if (e < E) {
+      const float x = __ldcg(z + (size_t)t * ld + e) + (bias != nullptr ? bias[e] : 0.f);
+      v[i] = score == 1 ? 1.0f / (1.0f + expf(-x)) : x;
+    }
+  }
+  if (score == 1 && groups > 1) {
+    // a group's score: the sum of its two largest (a group of one: that one); the `keep`
+    // best groups stay, the lower index among equals
+    const int per = E / groups;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (lane + 32 * i < E) s_all[lane + 32 * i] = v[i];
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;
+      for (int k = 0; k < per; ++k) {
+        const float x = s_all[g * per + k];
+        if (x > a) { b = a; a = x; } else if (x > b) { b = x; }
+      }
+      s_group[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    for (int c = 0; c < keep; ++c) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32)
+        if (s_group[g] > best) { best = s_group[g]; at = g; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+      }
+      __syncwarp();
+      if (lane == 0 && at < groups) s_group[at] = INFINITY;  // kept (a sum of scores is finite)
+      __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && s_group[e / per] != INFINITY) v[i] = -INFINITY;
+    }
   }
   float first = 0.f, sum = 0.f, mine = 0.f;
   for (int c = 0; c < top; ++c) {  // top <= 32: lane c keeps the c-th chosen value
@@ -46,7 +95,7 @@ __global__ void moe_route_kernel(const float* z, long long ld, const float* __re
       if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
     }
     if (c == 0) first = best;  // values are chosen in falling order: the first is the largest
-    const float e = expf(best - first);
+    const float e = score == 1 ? best : expf(best - first);
     sum += e;
     if (lane == c) mine = e;
     if (at >= E) at = 0;  // only when every value left is NaN: any expert, never a wild index
@@ -55,7 +104,7 @@ __global__ void moe_route_kernel(const float* z, long long ld, const float* __re
     for (int i = 0; i < 8; ++i)
       if (at == lane + 32 * i) v[i] = -INFINITY;
   }
-  if (lane < top) weights[(size_t)t * top + lane] = mine / sum;
+  if (lane < top) weights[(size_t)t * top + lane] = score == 1 ? mine : mine / sum;
 }
 
 template <typename T>
@@ -92,7 +141,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_experts_rows_kernel(const T* h, const T* __restrict__ gate_up, const T* __restrict__ down,
                         const int* chosen, const float* weights, float* __restrict__ out, int W,
-                        int ff, int top, int E, float limit, float alpha) {
+                        int ff, int top, int E, float limit, float alpha, float shift,
+                        const float* addend) {
   fb_pdl_wait();
   extern __shared__ float smem[];  // x [W] | act [ff] | acc [W]
   float* x = smem;
@@ -115,7 +165,7 @@ moe_experts_rows_kernel(const T* h, const T* __restrict__ gate_up, const T* __re
       float u = dot_row<T>(gu + (size_t)(ff + f) * W, x, W, lane);
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
-      if (lane == 0) act[f] = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+      if (lane == 0) act[f] = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift);
     }
     __syncthreads();
     const T* dn = down + (size_t)e * W * ff;
@@ -125,24 +175,33 @@ moe_experts_rows_kernel(const T* h, const T* __restrict__ gate_up, const T* __re
     }
     __syncthreads();
   }
-  for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)t * W + i] = acc[i];
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    out[(size_t)t * W + i] =
+        acc[i] + (addend != nullptr ? __ldcg(addend + (size_t)t * W + i) : 0.f);
 }
 }  // namespace
 
 FB_API int fb_moe_route(const float* z, long long ld, const float* bias, int E, int top,
-                        int* chosen, float* weights, int T, cudaStream_t stream) {
+                        int* chosen, float* weights, int T, int score, int groups, int keep,
+                        cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && E > 0 && E <= 256 && top > 0 && top <= E && top <= 32 && ld >= E,
              "moe_route: %d experts (at most 256), %d chosen (at most 32)", E, top);
+  FB_REQUIRE(score == 0 || score == 1, "moe_route: unknown scoring rule %d", score);
+  FB_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups &&
+             (long long)keep * (E / groups) >= top,
+             "moe_route: %d groups of %d experts, %d kept, %d chosen", groups, E, keep, top);
+  FB_REQUIRE(score == 1 || groups == 1, "moe_route: groups need the sigmoid scores");
   if (T == 0) return 0;
   // a warp per token
-  fb_launch(moe_route_kernel, dim3(T), dim3(32), 0, stream, z, ld, bias, E, top, chosen, weights);
+  fb_launch(moe_route_kernel, dim3(T), dim3(32), 0, stream, z, ld, bias, E, top, chosen, weights,
+            score, groups, keep);
   return fb_check_launch("moe_route");
 }
 
 FB_API int fb_moe_experts_rows(const void* h, int dtype, const void* gate_up, const void* down,
                                const int* chosen, const float* weights, float* out, int T, int W,
-                               int ff, int top, int E, float limit, float alpha,
-                               cudaStream_t stream) {
+                               int ff, int top, int E, float limit, float alpha, float shift,
+                               const float* addend, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && W > 0 && ff > 0 && top > 0, "moe_experts_rows: bad sizes");
   const size_t smem = (size_t)(2 * W + ff) * 4;
   FB_REQUIRE(smem <= 200 * 1024, "moe_experts_rows: width %d and %d hidden units do not fit "
@@ -156,7 +215,7 @@ FB_API int fb_moe_experts_rows(const void* h, int dtype, const void* gate_up, co
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);            \
     fb_launch(moe_experts_rows_kernel<E_>, dim3(T), dim3(256), smem, stream, (const E_*)h,      \
               (const E_*)gate_up, (const E_*)down, chosen, weights, out, W, ff, top, E, limit,  \
-              alpha);                                                                           \
+              alpha, shift, addend);                                                            \
   } while (0)
   FB_DISPATCH_DTYPE(dtype, E_, FB_MOE_ROWS(E_));
 #undef FB_MOE_ROWS
@@ -238,14 +297,14 @@ __global__ void moe_gather_kernel(const T* x, const int* pair_at, const int* sta
   for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)at * W + i] = x[(size_t)t * W + i];
 }
 
-__device__ __forceinline__ float glu_act(float g, float u, float limit, float alpha) {
+__device__ __forceinline__ float glu_act(float g, float u, float limit, float alpha, float shift) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
-  return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+  return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift);
 }
 
 template <typename TI, typename TO>
-__global__ void moe_glu_kernel(const TI* gu, TO* __restrict__ out, int ff, float limit, float alpha,
+__global__ void moe_glu_kernel(const TI* gu, TO* __restrict__ out, int ff, float limit, float alpha, float shift,
                                const int* starts, int E) {
   fb_pdl_launch();
   fb_pdl_wait();
@@ -254,7 +313,7 @@ __global__ void moe_glu_kernel(const TI* gu, TO* __restrict__ out, int ff, float
   for (int f = threadIdx.x; f < ff; f += blockDim.x)
     out[row * ff + f] = fb_from_float<TO>(glu_act(fb_load_coherent<TI>(gu + row * 2 * ff + f),
                                                   fb_load_coherent<TI>(gu + row * 2 * ff + ff + f),
-                                                  limit, alpha));
+                                                  limit, alpha, shift));
 }
 
 // 8 consecutive weights of a row as floats
@@ -289,7 +348,7 @@ template <typename T, typename TX, bool GATED, int CHUNK>
 __global__ void __launch_bounds__(256, 2)
 moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const int* starts,
                    float* __restrict__ out, long long ldo, int K, int N, int rows_per_block,
-                   float limit, float alpha, const int* pair_at, int top) {
+                   float limit, float alpha, float shift, const int* pair_at, int top) {
   fb_pdl_wait();
   extern __shared__ float xs[];  // [CHUNK][K]
   const int e = blockIdx.x;
@@ -365,7 +424,7 @@ moe_grouped_kernel(const TX* x, long long ldx, const T* __restrict__ w, const in
           const float g = fb_warp_sum(acc[r]);
           const float u = GATED ? fb_warp_sum(acc2[r]) : 0.f;
           if (lane == 0)
-            out[(size_t)(c0 + r) * ldo + row] = GATED ? glu_act(g, u, limit, alpha) : g;
+            out[(size_t)(c0 + r) * ldo + row] = GATED ? glu_act(g, u, limit, alpha, shift) : g;
         }
       }
     }
@@ -399,7 +458,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(256)
 moe_grouped_mma_kernel(const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* __restrict__ w,
                        const int* starts, void* out, long long ldo, int K, int N, float limit,
-                       float alpha, const int* pair_at, int top) {
+                       float alpha, float shift, const int* pair_at, int top) {
   fb_pdl_wait();
   extern __shared__ __align__(16) __nv_bfloat16 xb[];  // [MMA_ROWS][K + MMA_PAD]
   const int e = blockIdx.x;
@@ -470,7 +529,7 @@ moe_grouped_mma_kernel(const __nv_bfloat16* x, long long ldx, const __nv_bfloat1
       if (row < N && n < nc) {
         if (GATED)
           reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(c0 + n) * ldo + row] =
-              __float2bfloat16_rn(glu_act(cg[i], cu[i], limit, alpha));
+              __float2bfloat16_rn(glu_act(cg[i], cu[i], limit, alpha, shift));
         else
           reinterpret_cast<float*>(out)[(size_t)(c0 + n) * ldo + row] = cg[i];
       }
@@ -478,8 +537,10 @@ moe_grouped_mma_kernel(const __nv_bfloat16* x, long long ldx, const __nv_bfloat1
   }
 }
 
+// out[t] = sum_c weights[t, c] * y[place[t, c]] (+ addend[t], what every token gets
+// beside its experts: a shared expert's rows)
 __global__ void moe_combine_kernel(const float* y, const int* place, const float* weights, int top,
-                                   float* __restrict__ out, int W) {
+                                   float* __restrict__ out, int W, const float* addend) {
   fb_pdl_launch();
   fb_pdl_wait();
   const size_t t = blockIdx.x;
@@ -489,6 +550,7 @@ __global__ void moe_combine_kernel(const float* y, const int* place, const float
       const int at = place[t * top + c];
       if (at >= 0) acc = fmaf(weights[t * top + c], __ldcg(y + (size_t)at * W + i), acc);
     }
+    if (addend != nullptr) acc += __ldcg(addend + t * W + i);
     out[t * W + i] = acc;
   }
 }
@@ -512,12 +574,12 @@ FB_API int fb_moe_gather(const void* x, int dtype, const int* pair_at, const int
 }
 
 FB_API int fb_moe_glu(const void* gu, int in_dtype, void* out, int out_dtype, int n_pairs, int ff,
-                      float limit, float alpha, const int* starts, int E, cudaStream_t stream) {
+                      float limit, float alpha, float shift, const int* starts, int E, cudaStream_t stream) {
   FB_REQUIRE(n_pairs >= 0 && ff > 0, "moe_glu: bad sizes");
   if (n_pairs == 0) return 0;
   FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, TO, (fb_launch(
       moe_glu_kernel<TI, TO>, dim3(n_pairs), dim3(256), 0, stream, (const TI*)gu, (TO*)out, ff,
-      limit, alpha, starts, E))));
+      limit, alpha, shift, starts, E))));
   return fb_check_launch("moe_glu");
 }
 
@@ -525,7 +587,7 @@ FB_API int fb_moe_glu(const void* gu, int in_dtype, void* out, int out_dtype, in
 // gated = 0: x rows are float32 (the activations), w = down [E, N, K], out = products
 FB_API int fb_moe_grouped(int gated, const void* x, long long ldx, const void* w, int w_dtype,
                           const int* starts, float* out, long long ldo, int E, int K, int N,
-                          float limit, float alpha, int sm_count, const int* pair_at, int top,
+                          float limit, float alpha, float shift, int sm_count, const int* pair_at, int top,
                           int n_pairs, cudaStream_t stream) {
   FB_REQUIRE(E > 0 && K > 0 && N > 0 && ldx >= K && ldo >= N, "moe_grouped: bad sizes");
   FB_REQUIRE(K % 8 == 0 && ((uintptr_t)w % 16) == 0 && ldx % 4 == 0,
@@ -547,7 +609,7 @@ FB_API int fb_moe_grouped(int gated, const void* x, long long ldx, const void* w
       cudaFuncSetAttribute(moe_grouped_kernel<T_, TX_, G_, C_>,                                 \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);            \
     fb_launch(moe_grouped_kernel<T_, TX_, G_, C_>, grid, dim3(256), smem, stream,               \
-              (const TX_*)x, ldx, (const T_*)w, starts, out, ldo, K, N, rows, limit, alpha,     \
+              (const TX_*)x, ldx, (const T_*)w, starts, out, ldo, K, N, rows, limit, alpha, shift,     \
               pair_at, top);                                                                    \
   } while (0)
 #define FB_MOE_GROUPED(T_, TX_, G_)                                                             \
@@ -567,7 +629,7 @@ FB_API int fb_moe_grouped(int gated, const void* x, long long ldx, const void* w
 // gated = 1: out is bfloat16 activations [pairs, N]; gated = 0: out is float32 [pairs, N].
 FB_API int fb_moe_grouped_mma(int gated, const void* x, long long ldx, const void* w,
                               const int* starts, void* out, long long ldo, int E, int K, int N,
-                              float limit, float alpha, const int* pair_at, int top,
+                              float limit, float alpha, float shift, const int* pair_at, int top,
                               cudaStream_t stream) {
   FB_REQUIRE(E > 0 && K > 0 && N > 0 && ldx >= K && ldo >= N, "moe_grouped_mma: bad sizes");
   FB_REQUIRE(K % 64 == 0 && ldx % 8 == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)x % 16) == 0,
@@ -584,7 +646,7 @@ FB_API int fb_moe_grouped_mma(int gated, const void* x, long long ldx, const voi
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     fb_launch(moe_grouped_mma_kernel<true>, grid, dim3(256), smem, stream,
               (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, starts, out, ldo, K, N, limit,
-              alpha, pair_at, top);
+              alpha, shift, pair_at, top);
   } else {
     static bool seen[64];
     if (fb_first_use_on_device(seen))
@@ -592,15 +654,15 @@ FB_API int fb_moe_grouped_mma(int gated, const void* x, long long ldx, const voi
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     fb_launch(moe_grouped_mma_kernel<false>, grid, dim3(256), smem, stream,
               (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, starts, out, ldo, K, N, limit,
-              alpha, pair_at, top);
+              alpha, shift, pair_at, top);
   }
   return fb_check_launch("moe_grouped_mma");
 }
 
 FB_API int fb_moe_combine(const float* y, const int* place, const float* weights, int top,
-                          float* out, int T, int W, cudaStream_t stream) {
+                          float* out, int T, int W, const float* addend, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && W > 0 && top > 0, "moe_combine: bad sizes");
   if (T == 0) return 0;
-  fb_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, y, place, weights, top, out, W);
+  fb_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, y, place, weights, top, out, W, addend);
   return fb_check_launch("moe_combine");
 }

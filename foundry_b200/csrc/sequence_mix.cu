@@ -5,6 +5,8 @@
 //   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 // RWKV-style time mixing with a bonus for the current token (per head):
 //   o = (S + diag(b) k v^T)^T r;  S <- diag(w) S + k v^T
+// State-space duality (Mamba-2) with one decay a head, a step size and a skip (per head):
+//   S <- g S + k (step v)^T;  o = S^T q + skip v
 //
 // Both recurrences act on the columns of S independently, so a thread owns a
 // slice of one column in registers (16 consecutive key rows at most, a column
@@ -85,12 +87,12 @@ __global__ void state_tail_update_kernel(const T* x, long long ld, float* state,
 }
 
 // ------------------------------------- causal convolution + SiLU + unit heads
-// y[t, c] = silu(sum_a w[c, a] x[t - (taps - 1 - a), c]); rows in front of the
+// y[t, c] = silu(sum_a w[c, a] x[t - (taps - 1 - a), c] + bias[c]) (bias optional); rows in front of the
 // step come from the state's tail, which holds zeros at a sequence's start.
 // Then the first `n_unit` heads of `dim` channels are scaled to unit length,
 // x / sqrt(sum(x^2) + unit_eps), the first `n_scaled` of them also by `extra`.
 __global__ void conv_silu_unit_kernel(const float* x, long long ld, const float* __restrict__ w,
-                                      int taps, float* state, long long state_stride,
+                                      const float* __restrict__ bias, int taps, float* state, long long state_stride,
                                       long long tail_offset, float* __restrict__ out, int C,
                                       const int* __restrict__ seq_of_token,
                                       const int* __restrict__ cu_tokens,
@@ -119,6 +121,7 @@ __global__ void conv_silu_unit_kernel(const float* x, long long ld, const float*
       // on by one input as it is read, a thread touching only its own channel
       if (single && a > 0) tail[(size_t)(a - 1) * C + c] = v;
     }
+    if (bias != nullptr) acc += bias[c];
     y[c] = acc * sigmoidf_(acc);
   }
   __syncthreads();
@@ -138,10 +141,11 @@ __global__ void conv_silu_unit_kernel(const float* x, long long ld, const float*
 // mode 0: out <- exp(-exp(A[head]) * softplus(x + bias[c]))   (c = head * per_head + channel;
 //         per_head = 1: one decay a head)
 // mode 1: out <- exp(-exp(x + bias[c]))
-// x has rows of stride ld, out is contiguous [T, n] (and may be x itself).
+// x has rows of stride ld, out is contiguous [T, n] (and may be x itself). `steps`
+// (mode 0, optional, contiguous [T, n]) receives softplus(x + bias[c]) itself.
 __global__ void decay_gate_kernel(const float* in, long long ld, float* out, long long n_total,
                                   int n, int per_head, const float* __restrict__ A,
-                                  const float* __restrict__ bias, int mode) {
+                                  const float* __restrict__ bias, int mode, float* steps) {
   fb_pdl_launch();
   fb_pdl_wait();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_total;
@@ -149,7 +153,13 @@ __global__ void decay_gate_kernel(const float* in, long long ld, float* out, lon
     const long long t = i / n;
     const int c = (int)(i - t * n);
     const float v = __ldcg(in + t * ld + c) + bias[c];
-    out[i] = mode == 0 ? expf(-expf(A[c / per_head]) * softplusf_(v)) : expf(-expf(v));
+    if (mode == 0) {
+      const float sp = softplusf_(v);
+      out[i] = expf(-expf(A[c / per_head]) * sp);
+      if (steps != nullptr) steps[i] = sp;
+    } else {
+      out[i] = expf(-expf(v));
+    }
   }
 }
 
@@ -161,8 +171,9 @@ struct ScanArgs {
   const float* k; long long k_ld;   // keys, same head mapping
   const float* v; long long v_ld;   // values: head h at h * vdim
   const float* g; long long g_ld;   // decays: head h at h * dim, or one per head at h (g_scalar)
-  const float* beta; long long beta_ld;  // delta: raw step size per head (sigmoid applied here)
-  const float* bonus;               // wkv: [H, dim]
+  const float* beta; long long beta_ld;  // delta: raw step size per head (sigmoid applied here);
+                                    // ssd: the step size per head as it is
+  const float* bonus;               // wkv: [H, dim]; ssd: the skip, [H]
   float* state; long long state_stride; long long s_offset;
   float* out;                       // [T, H * vdim]
   const int* cu_tokens; const int* slots;
@@ -238,7 +249,7 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc) {
         src = a.v + (size_t)h * vdim + col0 + (c - 3 * dimp);
         step = a.v_ld;
       }
-    } else if (MODE == 0 && c == 3 * dimp + cols_blk) {
+    } else if (MODE != 1 && c == 3 * dimp + cols_blk) {
       src = a.beta + h;
       step = a.beta_ld;
     }
@@ -263,6 +274,7 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc) {
     }
   };
 
+  const float skip = MODE == 2 ? a.bonus[h] : 0.f;
   float s[RP], bonus[RP];
 #pragma unroll
   for (int i = 0; i < RP; ++i) {
@@ -311,6 +323,18 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc) {
             o4[2] = fmaf(s[i + 2], q.z, o4[2]); o4[3] = fmaf(s[i + 3], q.w, o4[3]);
           }
         }
+      } else if (MODE == 2) {
+        const float u = tok[3 * dimp + cols_blk] * v;  // step size times the value
+#pragma unroll
+        for (int i = 0; i < RP; i += 4) {
+          {
+            const float4 g = g4[i / 4], k = k4[i / 4], q = q4[i / 4];
+            s[i] = fmaf(k.x, u, g.x * s[i]); s[i + 1] = fmaf(k.y, u, g.y * s[i + 1]);
+            s[i + 2] = fmaf(k.z, u, g.z * s[i + 2]); s[i + 3] = fmaf(k.w, u, g.w * s[i + 3]);
+            o4[0] = fmaf(s[i], q.x, o4[0]); o4[1] = fmaf(s[i + 1], q.y, o4[1]);
+            o4[2] = fmaf(s[i + 2], q.z, o4[2]); o4[3] = fmaf(s[i + 3], q.w, o4[3]);
+          }
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < RP; i += 4) {
@@ -333,6 +357,8 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc) {
       float o = 0.f;
 #pragma unroll
       for (int p = 0; p < KP; ++p) o += opart[r * 32 + p * COLS_W + (lane % COLS_W)];
+      if (MODE == 2)  // the skip: the token's own value straight to its output
+        o = fmaf(skip, sbuf[(size_t)buf * tc * per_tok + (size_t)r * per_tok + 3 * dimp + jl], o);
       if (col) a.out[(size_t)(start + c0 + r) * a.H * vdim + (size_t)h * vdim + j] = o;
     }
     __syncthreads();  // the buffers are refilled by the next iteration
@@ -346,11 +372,15 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc) {
 
 // ------------------------------------------------- per-head RMS norm and gate
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[h * w_stride + :] * act(gate[t, h, :])
-// act: 0 sigmoid, 1 SiLU.
+// act: 0 sigmoid, 1 SiLU. `gate_first`: the gate comes before the norm,
+// out = y / sqrt(mean(y^2) + eps) * w with y = o * act(gate). A "head" is any equal part
+// of the row that is normalised by itself. Output rows lie `out_ld` elements apart and
+// are multiplied by `out_scale` before they are rounded.
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* o, const float* __restrict__ w, int w_stride,
                                       const float* gate, long long gate_ld, int act, float eps,
-                                      T* __restrict__ out, int H, int vdim) {
+                                      T* __restrict__ out, long long out_ld, float out_scale,
+                                      int H, int vdim, int gate_first) {
   fb_pdl_launch();
   fb_pdl_wait();
   const int t = blockIdx.x;
@@ -359,20 +389,24 @@ __global__ void head_norm_gate_kernel(const float* o, const float* __restrict__ 
     const float* row = o + ((size_t)t * H + h) * vdim;
     float ss = 0.f;
     for (int d = lane; d < vdim; d += 32) {
-      const float v = __ldcg(row + d);
+      float v = __ldcg(row + d);
+      if (gate_first) {
+        const float gz = __ldcg(gate + (size_t)t * gate_ld + (size_t)h * vdim + d);
+        v *= act == 0 ? sigmoidf_(gz) : gz * sigmoidf_(gz);
+      }
       ss += v * v;
     }
     const float r = 1.0f / sqrtf(fb_warp_sum(ss) / (float)vdim + eps);
     for (int d = lane; d < vdim; d += 32) {
       const float gz = __ldcg(gate + (size_t)t * gate_ld + (size_t)h * vdim + d);
       const float ga = act == 0 ? sigmoidf_(gz) : gz * sigmoidf_(gz);
-      out[((size_t)t * H + h) * vdim + d] =
-          fb_from_float<T>(__ldcg(row + d) * r * w[(size_t)h * w_stride + d] * ga);
+      out[(size_t)t * out_ld + (size_t)h * vdim + d] =
+          fb_from_float<T>(__ldcg(row + d) * r * w[(size_t)h * w_stride + d] * ga * out_scale);
     }
   }
 }
 
-// out = act(in) rounded to the activation type; act: 0 identity, 1 tanh
+// out = act(in) rounded to the activation type; act: 0 identity, 1 tanh, 2 the square of relu
 template <typename T>
 __global__ void unary_cast_kernel(const float* in, long long ld, T* __restrict__ out, int n,
                                   int act) {
@@ -381,7 +415,8 @@ __global__ void unary_cast_kernel(const float* in, long long ld, T* __restrict__
   const size_t t = blockIdx.x;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float v = __ldcg(in + t * ld + i);
-    out[t * n + i] = fb_from_float<T>(act == 1 ? tanhf(v) : v);
+    const float r = fmaxf(v, 0.f);
+    out[t * n + i] = fb_from_float<T>(act == 1 ? tanhf(v) : act == 2 ? r * r : v);
   }
 }
 }  // namespace
@@ -410,7 +445,7 @@ FB_API int fb_state_tail_update(const void* x, int dtype, long long ld, float* s
   return fb_check_launch("state_tail_update");
 }
 
-FB_API int fb_conv_silu_unit(const float* x, long long ld, const float* w, int taps,
+FB_API int fb_conv_silu_unit(const float* x, long long ld, const float* w, const float* bias, int taps,
                              float* state, long long state_stride, long long tail_offset,
                              float* out, int C, const int* seq_of_token, const int* cu_tokens,
                              const int* slots, int n_unit, int dim, int n_scaled, float extra,
@@ -428,21 +463,22 @@ FB_API int fb_conv_silu_unit(const float* x, long long ld, const float* w, int t
   // few tokens: wide blocks, so that a token's loads are many threads' and not one
   // thread's one after another
   const int threads = (T <= 64 && C >= 2048) ? 1024 : 256;
-  fb_launch(conv_silu_unit_kernel, dim3(T), dim3(threads), smem, stream, x, ld, w, taps, state,
+  fb_launch(conv_silu_unit_kernel, dim3(T), dim3(threads), smem, stream, x, ld, w, bias, taps, state,
             state_stride, tail_offset, out, C, seq_of_token, cu_tokens, slots, n_unit, dim,
             n_scaled, extra, unit_eps, single);
   return fb_check_launch("conv_silu_unit");
 }
 
 FB_API int fb_decay_gate(const float* x, long long ld, float* out, int T, int n, int per_head,
-                         const float* A, const float* bias, int mode, cudaStream_t stream) {
+                         const float* A, const float* bias, int mode, float* steps,
+                         cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && n > 0 && per_head > 0 && bias != nullptr && (mode == 1 || A != nullptr) &&
              ld >= n, "decay_gate: bad arguments");
   if (T == 0) return 0;
   const long long total = (long long)T * n;
   const int blocks = (int)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048);
   fb_launch(decay_gate_kernel, dim3(blocks), dim3(256), 0, stream, x, ld, out, total, n, per_head,
-            A, bias, mode);
+            A, bias, mode, steps);
   return fb_check_launch("decay_gate");
 }
 
@@ -465,11 +501,13 @@ FB_API int fb_state_scan(int mode, const float* q, long long q_ld, const float* 
                          const int* cu_tokens, const int* slots, int n_seqs, int H, int rep,
                          int dim, int vdim, int g_scalar, int serial_launch, cudaStream_t stream) {
   const bool serial = serial_launch != 0;
-  FB_REQUIRE(mode == 0 || mode == 1, "state_scan: unknown recurrence %d", mode);
+  FB_REQUIRE(mode >= 0 && mode <= 2, "state_scan: unknown recurrence %d", mode);
+  FB_REQUIRE(mode != 2 || g_scalar, "state_scan: the state-space recurrence takes one decay a head");
   FB_REQUIRE(n_seqs >= 0 && H > 0 && rep > 0 && H % rep == 0 && dim > 0 && vdim > 0,
              "state_scan: bad sizes");
   FB_REQUIRE(dim <= R * 32, "state_scan: %d key channels exceed %d", dim, R * 32);
-  FB_REQUIRE(mode == 0 ? beta != nullptr : bonus != nullptr, "state_scan: a missing input");
+  FB_REQUIRE((mode == 1 || beta != nullptr) && (mode == 0 || bonus != nullptr),
+             "state_scan: a missing input");
   if (n_seqs == 0) return 0;
   ScanArgs a{q, q_ld, k, k_ld, v, v_ld, g, g_ld, beta, beta_ld, bonus, state, state_stride,
              s_offset, out, cu_tokens, slots, H, rep, dim, vdim, g_scalar ? 1 : 0};
@@ -514,11 +552,11 @@ FB_API int fb_state_scan(int mode, const float* q, long long q_ld, const float* 
   } while (0)
 #define FB_SCAN(KP_)                                                \
   case KP_:                                                         \
-    if (rp == 4) { if (mode == 0) FB_SCAN_MINE(0, KP_, 4); else FB_SCAN_MINE(1, KP_, 4); } \
-    else { if (mode == 0) FB_SCAN_MINE(0, KP_, 8); else FB_SCAN_MINE(1, KP_, 8); }         \
+    if (rp == 4) { if (mode == 0) FB_SCAN_MINE(0, KP_, 4); else if (mode == 1) FB_SCAN_MINE(1, KP_, 4); else FB_SCAN_MINE(2, KP_, 4); } \
+    else { if (mode == 0) FB_SCAN_MINE(0, KP_, 8); else if (mode == 1) FB_SCAN_MINE(1, KP_, 8); else FB_SCAN_MINE(2, KP_, 8); }         \
     break;
   if (kp == 32 && rp == 16) {
-    if (mode == 0) FB_SCAN_MINE(0, 32, 16); else FB_SCAN_MINE(1, 32, 16);
+    if (mode == 0) FB_SCAN_MINE(0, 32, 16); else if (mode == 1) FB_SCAN_MINE(1, 32, 16); else FB_SCAN_MINE(2, 32, 16);
   } else {
     switch (kp) {
       FB_SCAN(1) FB_SCAN(2) FB_SCAN(4) FB_SCAN(8) FB_SCAN(16) FB_SCAN(32)
@@ -532,12 +570,14 @@ FB_API int fb_state_scan(int mode, const float* q, long long q_ld, const float* 
 }
 
 FB_API int fb_head_norm_gate(const float* o, const float* w, int w_stride, const float* gate,
-                             long long gate_ld, int act, float eps, void* out, int dtype, int T,
-                             int H, int vdim, cudaStream_t stream) {
+                             long long gate_ld, int act, float eps, void* out, long long out_ld,
+                             float out_scale, int dtype, int T, int H, int vdim, int gate_first,
+                             cudaStream_t stream) {
+  FB_REQUIRE(out_ld >= (long long)H * vdim, "head_norm_gate: output rows of %lld are too short", out_ld);
   FB_REQUIRE(T >= 0 && H > 0 && vdim > 0 && (act == 0 || act == 1), "head_norm_gate: bad sizes");
   if (T == 0) return 0;
   FB_DISPATCH_DTYPE(dtype, E, (fb_launch(head_norm_gate_kernel<E>, dim3(T), dim3(256), 0, stream,
-      o, w, w_stride, gate, gate_ld, act, eps, (E*)out, H, vdim)));
+      o, w, w_stride, gate, gate_ld, act, eps, (E*)out, out_ld, out_scale, H, vdim, gate_first)));
   return fb_check_launch("head_norm_gate");
 }
 

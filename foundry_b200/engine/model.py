@@ -4,7 +4,8 @@ over a step's tokens.
 Order of work (src/models/llama/model.rs:168-193 and 102-122): gather the
 token embeddings; run the schedule's layers; keep only the rows whose logits
 are wanted; final norm; output head (the embedding table when the description
-names no separate head, model.rs:62). The residual stream is float32.
+names no separate head, model.rs:62); a soft cap on the logits where the
+description gives one. The residual stream is float32.
 """
 from __future__ import annotations
 
@@ -17,6 +18,7 @@ from ..config.spec import ModelSpec
 from ..kernels import ops
 from ..parts import BLOCKS, EMBEDDINGS, JUNCTIONS, NORMS
 from ..parts.base import first_weight_of
+from ..parts.block import EMBEDDING_OUTPUT
 from ..parts.linear import matmul_nt
 from ..weights.loader import ExpectedTensor, check_against, load_tensor
 from ..weights.safetensors_io import WeightFiles
@@ -150,14 +152,17 @@ class Model:
             shared.clear()  # what an earlier step on this context left
         resid = torch.empty((ctx.n_tokens, spec.hidden_size), dtype=torch.float32,
                             device=self.device)
-        # a junction may read the stream as the embedding left it
-        x0 = torch.empty_like(resid) if self.junctions else None
+        # a junction or a block may read the stream as the embedding left it
+        keeps = any(getattr(b, "needs_embedding_output", False) for b in self.blocks)
+        x0 = torch.empty_like(resid) if self.junctions or keeps else None
         if self.embedder is None:
             ops.embed_gather(self.embedding, ctx.token_ids, resid)
             if x0 is not None:
                 x0.copy_(resid)
         else:
             self.embedder.forward(ctx, self.embedding, resid, x0)
+        if keeps:
+            ctx.shared[EMBEDDING_OUTPUT] = x0
         delta = None
         for i, entry in enumerate(spec.schedule):
             block = self.blocks[entry.layer]
@@ -178,6 +183,8 @@ class Model:
         logits = torch.empty((n, spec.vocab_size), dtype=torch.float32, device=self.device)
         if n == 0:
             return logits
+        if isinstance(delta, ops.DepthMix):  # the last stream is a sum over the kept ones
+            delta = delta.settle(resid)
         rows = torch.empty((n, spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.gather_rows(resid, ctx.want_rows, rows)
         rows_delta = None
@@ -198,4 +205,7 @@ class Model:
             if scale is not None:
                 rows_delta = ops.ScaledDelta(rows_delta, scale)
         normed = self.final_norm.add_norm(rows, rows_delta)
-        return matmul_nt(normed, self.output_head, logits)
+        matmul_nt(normed, self.output_head, logits)
+        if spec.logit_softcap is not None:  # logits <- cap * tanh(logits / cap)
+            ops.softcap(logits, spec.logit_softcap)
+        return logits

@@ -87,7 +87,16 @@ _SIGNATURES = {
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_void_p, c_void_p, c_void_p],
     "fb_ln_add_ln": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                     c_int, c_int, c_int, c_float, c_void_p],
+                     c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "fb_softcap": [c_void_p, c_ll, c_float, c_void_p],
+    "fb_head_norm_rope_cache_write": [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_float,
+                                      c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                      c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int, c_int,
+                                      c_int, c_int, c_int, c_int, c_void_p],
+    "fb_attention_sigmoid": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
+                             c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_void_p, c_void_p,
+                             c_ll, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_void_p],
     "fb_embed_sinusoid": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_void_p],
     "fb_concat_cast": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -124,30 +133,34 @@ _SIGNATURES = {
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "fb_state_tail_update": [c_void_p, c_int, c_ll, c_void_p, c_ll, c_ll, c_int, c_int, c_void_p,
                              c_void_p, c_int, c_void_p],
-    "fb_conv_silu_unit": [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_ll, c_ll, c_void_p, c_int,
+    "fb_conv_silu_unit": [c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_ll, c_void_p, c_int,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
                           c_int, c_int, c_void_p],
     "fb_decay_gate": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
-                      c_void_p],
+                      c_void_p, c_void_p],
     "fb_state_scan": [c_int, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll,
                       c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_float, c_void_p,
-                          c_int, c_int, c_int, c_int, c_void_p],
+                          c_ll, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_unary_cast": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "fb_moe_route": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "fb_moe_route": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                     c_int, c_void_p],
     "fb_moe_experts_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+                            c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p,
+                            c_void_p],
     "fb_moe_sort": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "fb_moe_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                       c_void_p],
-    "fb_moe_glu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p,
-                   c_int, c_void_p],
+    "fb_moe_glu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float,
+                   c_void_p, c_int, c_void_p],
     "fb_moe_grouped": [c_int, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_ll, c_int,
-                       c_int, c_int, c_float, c_float, c_int, c_void_p, c_int, c_int, c_void_p],
+                       c_int, c_int, c_float, c_float, c_float, c_int, c_void_p, c_int, c_int,
+                       c_void_p],
     "fb_moe_grouped_mma": [c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
-                           c_int, c_float, c_float, c_void_p, c_int, c_void_p],
-    "fb_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+                           c_int, c_float, c_float, c_float, c_void_p, c_int, c_void_p],
+    "fb_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
+                       c_void_p],
 }
 
 _FUNCS = {}
@@ -1585,9 +1598,31 @@ class NormedDelta:
         return None
 
 
+class DepthMix:
+    """A stream that is still to be replaced by a weighted sum over the streams
+    the layers so far have left: with X_0 = `first`, X_1 .. X_(n-1) the first rows
+    of `kept` ([>= n, T, W]) and X_n = resid + LN(pending) (kept as row n - 1 of
+    `kept`), resid <- sum_j weights[j] X_j. The layer norm that follows in the
+    stream does it in its own pass over the row (`ln_add_ln`); `settle` does it alone."""
+
+    def __init__(self, pending: Optional["NormedDelta"], first: torch.Tensor, kept: torch.Tensor,
+                 weights: torch.Tensor, n: int):
+        self.pending, self.first, self.kept, self.weights, self.n = pending, first, kept, weights, n
+
+    @property
+    def eps(self) -> float:
+        return self.pending.eps if self.pending is not None else 0.0
+
+    def settle(self, resid: torch.Tensor) -> None:
+        ln_add_ln(resid, self.pending, None, None, self.eps or 1.0, None, mix=self)
+        return None
+
+
 def ln_add_ln(resid: torch.Tensor, pending: Optional[NormedDelta], weight: Optional[torch.Tensor],
-              bias: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor]):
-    """resid += LN(pending.values) where `pending` is given, then
+              bias: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor],
+              mix: Optional[DepthMix] = None):
+    """resid += LN(pending.values) where `pending` is given, then (with `mix`) resid is kept
+    and replaced by the weighted sum over the kept streams, then
     out = LN(resid; weight, bias) where `out` is given; float32 statistics."""
     T, W = resid.shape
     y = w1 = b1 = 0
@@ -1607,9 +1642,25 @@ def ln_add_ln(resid: torch.Tensor, pending: Optional[NormedDelta], weight: Optio
             raise KernelError(f"ln_add_ln: out {tuple(out.shape)}, weight {tuple(weight.shape)}")
         o, o_code = _dev(out, "out"), code_of(out.dtype)
         w2, b2 = _dev(weight, "weight", torch.float32), _dev(bias, "bias", torch.float32)
+    m_first = m_kept = m_weights = m_n = 0
+    if mix is not None:
+        n = int(mix.n)
+        if (tuple(mix.first.shape) != (T, W) or mix.kept.dim() != 3 or mix.kept.shape[0] < n
+                or tuple(mix.kept.shape[1:]) != (T, W) or mix.weights.numel() != n + 1 or n < 1):
+            raise KernelError(f"ln_add_ln: a depth-wise average of {n} kept streams "
+                              f"{tuple(mix.kept.shape)} with {mix.weights.numel()} weights")
+        m_first = _dev(mix.first, "first", torch.float32)
+        m_kept = _dev(mix.kept, "kept", torch.float32)
+        m_weights, m_n = _dev(mix.weights, "weights", torch.float32), n
     _call("fb_ln_add_ln", y, y_code, w1, b1, _dev(resid, "resid", torch.float32), w2, b2, o, o_code,
-          T, W, float(eps), _stream())
+          T, W, float(eps), m_first, m_kept, m_weights, m_n, _stream())
     return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _call("fb_softcap", _dev(x, "x", torch.float32), x.numel(), float(cap), _stream())
+    return x
 
 
 def embed_sinusoid(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
@@ -1940,6 +1991,66 @@ def attention_maps_rows(ctx, q: torch.Tensor, out: torch.Tensor, k: torch.Tensor
     return out
 
 
+# ------------------------------------------ attention with sigmoid weights in chunks
+def head_norm_rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor,
+                               wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
+                               value_norm: bool, freq: Optional[torch.Tensor], positions,
+                               seq_of_token, page_table, k_cache, v_cache, H: int, G: int,
+                               dim: int, vdim: int, write_cache: bool = True) -> torch.Tensor:
+    """Per-head RMS norms of queries and keys (weights [dim] shared by the heads, or
+    none), the rotation of their first 2 * len(freq) elements (element i with element
+    i + len(freq); `freq` float64), the values' RMS norm without weight where
+    `value_norm`; queries to `q_out`, keys and values into the token's cache row.
+    `qkv`: float32 rows [q | k | v]."""
+    T = qkv.shape[0]
+    kp = vp = 0
+    ks = vs = (0, 0)
+    if write_cache:
+        _check_kv_pair(k_cache, v_cache, G, dim, vdim, q_out.dtype)
+        kp, vp = k_cache.data_ptr(), v_cache.data_ptr()
+        ks, vs = (k_cache.stride(0), k_cache.stride(1)), (v_cache.stride(0), v_cache.stride(1))
+    rot = 0 if freq is None else 2 * freq.numel()
+    for name, w in (("wq", wq), ("wk", wk)):
+        if w is not None and tuple(w.shape) != (dim,):
+            raise KernelError(f"head_norm_rope_cache_write: {name} {tuple(w.shape)} for heads of {dim}")
+    _call("fb_head_norm_rope_cache_write", _dev(qkv, "qkv", torch.float32, contiguous=False),
+          _rows(qkv, "qkv"), _dev(q_out, "q_out"), code_of(q_out.dtype),
+          0 if wq is None else _dev(wq, "wq", torch.float32),
+          0 if wk is None else _dev(wk, "wk", torch.float32), float(eps), 1 if value_norm else 0,
+          0 if freq is None else _dev(freq, "freq", torch.float64), rot,
+          _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1], kp, vp, *ks, *vs,
+          T, H, G, dim, vdim, 1 if write_cache else 0, _stream())
+    return q_out
+
+
+def attention_sigmoid(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache, v_cache,
+                      H: int, G: int, dim: int, vdim: int, scale: float, chunk: int = 0,
+                      head_bias: Optional[torch.Tensor] = None,
+                      gate: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> torch.Tensor:
+    """out[t, head] = sigmoid(gate[t, head]) * sum over the visible keys j of
+    sigmoid(q . k_j * scale + head_bias[head]) v_j; j is visible iff j <= the token's
+    position and both lie in the same chunk of `chunk` positions (0: every j <=).
+    `gate`: float32 view [T, >= H] of raw gate values, or None (no gate). `out` may be a
+    view of rows that lie further apart; `out_scale` multiplies the output."""
+    T = q.shape[0]
+    _check_kv_pair(k_cache, v_cache, G, dim, vdim, q.dtype)
+    if head_bias is not None and tuple(head_bias.shape) != (H,):
+        raise KernelError(f"attention_sigmoid: {tuple(head_bias.shape)} biases for {H} heads")
+    _call("fb_attention_sigmoid", _dev(q, "q", contiguous=False), _rows(q, "q"),
+          _dev(out, "out", q.dtype, contiguous=False), _rows(out, "out"), code_of(q.dtype),
+          _dev(ctx.positions, "positions", torch.int32),
+          _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1],
+          k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
+          v_cache.stride(0), v_cache.stride(1),
+          0 if head_bias is None else _dev(head_bias, "head_bias", torch.float32),
+          0 if gate is None else _dev(gate, "gate", torch.float32, contiguous=False),
+          0 if gate is None else _rows(gate, "gate"), float(scale), float(out_scale),
+          int(chunk or 0), T, H, G, dim, vdim, _stream())
+    return out
+
+
 # ---------------------------------------------------- mixers with a carried state
 class StateRows:
     """One cache entry's state rows [slots, floats] seen as named float32
@@ -1986,19 +2097,22 @@ def state_tail_update(ctx, x: torch.Tensor, state: StateRows, field: str, n_tail
 
 
 def conv_silu_unit(ctx, x: torch.Tensor, weight: torch.Tensor, state: StateRows, field: str,
-                   out: torch.Tensor, channels: int, n_unit: int, dim: int, n_scaled: int,
-                   extra: float, unit_eps: float) -> bool:
+                   out: torch.Tensor, channels: int, n_unit: int = 0, dim: int = 1,
+                   n_scaled: int = 0, extra: float = 1.0, unit_eps: float = 0.0,
+                   bias: Optional[torch.Tensor] = None) -> bool:
     """Causal convolution over time per channel, SiLU, then unit-length heads
     (csrc/sequence_mix.cu). `x` float32 rows (first `channels` columns are used).
     Returns whether the kernel moved the state's tail on itself (a step of one
     token a sequence); otherwise `state_tail_update` has to follow."""
     T = x.shape[0]
     taps = weight.shape[1]
-    if weight.shape[0] != channels or out.shape != (T, channels):
+    if weight.shape[0] != channels or out.shape != (T, channels) or \
+            (bias is not None and bias.numel() != channels):
         raise KernelError("conv_silu_unit: shapes differ")
     _call("fb_conv_silu_unit", _dev(x, "x", torch.float32, contiguous=False), _rows(x, "x"),
-          _dev(weight, "weight", torch.float32), taps, state.rows.data_ptr(), state.stride,
-          state.offset[field], _dev(out, "out", torch.float32), channels,
+          _dev(weight, "weight", torch.float32),
+          0 if bias is None else _dev(bias, "bias", torch.float32), taps, state.rows.data_ptr(),
+          state.stride, state.offset[field], _dev(out, "out", torch.float32), channels,
           _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
           _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.slots, "slots", torch.int32),
           n_unit, dim, n_scaled, float(extra), float(unit_eps), T, 1 if ctx.is_decode else 0,
@@ -2007,7 +2121,7 @@ def conv_silu_unit(ctx, x: torch.Tensor, weight: torch.Tensor, state: StateRows,
 
 
 def decay_gate(x: torch.Tensor, per_head: int, bias: torch.Tensor, A: Optional[torch.Tensor],
-               out: Optional[torch.Tensor] = None):
+               out: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None):
     """On float32 rows [T, n] (in place, or from a strided view `x` into the contiguous
     `out`): with `A` ([heads]) exp(-exp(A) softplus(x + bias)), one decay for every
     `per_head` channels' head (per_head 1: one a head); without it exp(-exp(x + bias))."""
@@ -2015,14 +2129,17 @@ def decay_gate(x: torch.Tensor, per_head: int, bias: torch.Tensor, A: Optional[t
     out = x if out is None else out
     if bias.numel() != n or tuple(out.shape) != (T, n):
         raise KernelError("decay_gate: the bias does not fit the rows")
+    if steps is not None and (A is None or tuple(steps.shape) != (T, n)):
+        raise KernelError("decay_gate: `steps` ([T, n], softplus(x + bias)) goes with `A`")
     _call("fb_decay_gate", _dev(x, "x", torch.float32, contiguous=False), _rows(x, "x"),
           _dev(out, "out", torch.float32), T, n, per_head,
           0 if A is None else _dev(A, "A", torch.float32), _dev(bias, "bias", torch.float32),
-          1 if A is None else 0, _stream())
+          1 if A is None else 0, 0 if steps is None else _dev(steps, "steps", torch.float32),
+          _stream())
     return out
 
 
-SCAN_DELTA, SCAN_WKV = 0, 1
+SCAN_DELTA, SCAN_WKV, SCAN_SSD = 0, 1, 2
 
 
 def state_scan(ctx, mode: int, q, k, v, g, state: StateRows, field: str, out: torch.Tensor,
@@ -2031,7 +2148,9 @@ def state_scan(ctx, mode: int, q, k, v, g, state: StateRows, field: str, out: to
     """The recurrence of csrc/sequence_mix.cu over every sequence of the step.
     q, k: float32 views [T, >= (H / rep) * dim]; v [T, >= H * vdim]; g [T, H * dim], or
     [T, H] with `decay_per_head` (one decay for all key channels of a head);
-    beta (delta) a float32 view [T, >= H]; bonus (wkv) [H, dim]; out float32 [T, H * vdim]."""
+    beta (delta) a float32 view [T, >= H]; bonus (wkv) [H, dim]; out float32 [T, H * vdim].
+    `SCAN_SSD`: S <- g S + k (beta v)^T; out = S^T q + bonus v, with one decay a head, `beta`
+    the step size as it is ([T, >= H]) and `bonus` the skip ([H])."""
     T = out.shape[0]
     if out.shape != (T, H * vdim) or out.dtype != torch.float32 or not out.is_contiguous():
         raise KernelError("state_scan: out must be contiguous float32 [T, heads * vdim]")
@@ -2050,13 +2169,18 @@ def state_scan(ctx, mode: int, q, k, v, g, state: StateRows, field: str, out: to
 
 
 def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, per_head_weight: bool, gate: torch.Tensor,
-                   act: str, eps: float, out: torch.Tensor, H: int, vdim: int) -> torch.Tensor:
-    """out = o / rms(o per head) * weight * act(gate); act "sigmoid" or "silu"."""
+                   act: str, eps: float, out: torch.Tensor, H: int, vdim: int,
+                   gate_first: bool = False, out_scale: float = 1.0) -> torch.Tensor:
+    """out = o / rms(o per head) * weight * act(gate); act "sigmoid" or "silu". With
+    `gate_first` the gate comes before the norm: y = o * act(gate), out = y / rms(y per
+    head) * weight. A "head" is any equal part of the row that is normalised by itself. `out`
+    may be a view of rows that lie further apart; `out_scale` multiplies the output."""
     T = o.shape[0]
     _call("fb_head_norm_gate", _dev(o, "o", torch.float32), _dev(weight, "weight", torch.float32),
           vdim if per_head_weight else 0, _dev(gate, "gate", torch.float32, contiguous=False),
-          _rows(gate, "gate"), {"sigmoid": 0, "silu": 1}[act], float(eps), _dev(out, "out"),
-          code_of(out.dtype), T, H, vdim, _stream())
+          _rows(gate, "gate"), {"sigmoid": 0, "silu": 1}[act], float(eps),
+          _dev(out, "out", contiguous=False), _rows(out, "out"), float(out_scale),
+          code_of(out.dtype), T, H, vdim, 1 if gate_first else 0, _stream())
     return out
 
 
@@ -2064,22 +2188,34 @@ def unary_cast(x: torch.Tensor, out: torch.Tensor, act: str = "identity") -> tor
     """out = act(x) rounded to out's dtype; x float32 rows (possibly strided)."""
     T, n = out.shape
     _call("fb_unary_cast", _dev(x, "x", torch.float32, contiguous=False), _rows(x, "x"),
-          _dev(out, "out"), code_of(out.dtype), T, n, {"identity": 0, "tanh": 1}[act], _stream())
+          _dev(out, "out"), code_of(out.dtype), T, n, {"identity": 0, "tanh": 1, "relu2": 2}[act], _stream())
     return out
 
 
 # ------------------------------------------------------------------ routed experts
-def moe_route(z: torch.Tensor, bias: torch.Tensor, top: int, chosen: torch.Tensor,
-              weights: torch.Tensor) -> None:
+MOE_SCORES = {"softmax_chosen": 0, "sigmoid": 1}
+
+
+def moe_route(z: torch.Tensor, bias: Optional[torch.Tensor], top: int, chosen: torch.Tensor,
+              weights: torch.Tensor, score: str = "softmax_chosen", groups: int = 1,
+              keep: int = 1) -> None:
+    """The `top` experts of every token and their weights from the router's float32
+    rows `z` (+ `bias`). "softmax_chosen": the largest z, weighted by the softmax over
+    the chosen ones. "sigmoid": scores sigmoid(z); of `groups` equal groups of
+    neighbouring experts only the `keep` with the largest sum of their two best scores
+    can be chosen; the weights are the chosen scores themselves."""
     T, E = z.shape
     _call("fb_moe_route", _dev(z, "z", torch.float32, contiguous=False), _rows(z, "z"),
-          _dev(bias, "bias", torch.float32), E, top, _dev(chosen, "chosen", torch.int32),
-          _dev(weights, "weights", torch.float32), T, _stream())
+          0 if bias is None else _dev(bias, "bias", torch.float32), E, top,
+          _dev(chosen, "chosen", torch.int32), _dev(weights, "weights", torch.float32), T,
+          MOE_SCORES[score], int(groups), int(keep), _stream())
 
 
 def moe_experts_rows(h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
                      chosen: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, limit: float,
-                     alpha: float) -> torch.Tensor:
+                     alpha: float, shift: float = 1.0,
+                     addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Every token streams its own experts; `addend` (float32 [T, W]) joins the sum."""
     T, W = h.shape
     E, two_ff, _ = gate_up.shape
     if gate_up.dtype != h.dtype or down.dtype != h.dtype or down.shape != (E, W, two_ff // 2):
@@ -2087,7 +2223,8 @@ def moe_experts_rows(h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
     _call("fb_moe_experts_rows", _dev(h, "h"), code_of(h.dtype), _dev(gate_up, "gate_up"),
           _dev(down, "down"), _dev(chosen, "chosen", torch.int32),
           _dev(weights, "weights", torch.float32), _dev(out, "out", torch.float32), T, W,
-          two_ff // 2, chosen.shape[1], E, float(limit), float(alpha), _stream())
+          two_ff // 2, chosen.shape[1], E, float(limit), float(alpha), float(shift),
+          0 if addend is None else _dev(addend, "addend", torch.float32), _stream())
     return out
 
 
@@ -2119,12 +2256,13 @@ def moe_gather(x: torch.Tensor, order: ExpertOrder) -> torch.Tensor:
 
 
 def moe_glu(gate_up: torch.Tensor, out: torch.Tensor, order: ExpertOrder, limit: float,
-            alpha: float) -> torch.Tensor:
-    """out = min(g, limit) * sigmoid(alpha min(g, limit)) * (clamp(u, +-limit) + 1) for rows
-    [g | u] of `gate_up`."""
+            alpha: float, shift: float = 1.0) -> torch.Tensor:
+    """out = min(g, limit) * sigmoid(alpha min(g, limit)) * (clamp(u, +-limit) + shift) for
+    rows [g | u] of `gate_up`."""
     n, two_ff = gate_up.shape
     _call("fb_moe_glu", _dev(gate_up, "gate_up"), code_of(gate_up.dtype), _dev(out, "out"),
-          code_of(out.dtype), n, two_ff // 2, float(limit), float(alpha), order.starts.data_ptr(),
+          code_of(out.dtype), n, two_ff // 2, float(limit), float(alpha), float(shift),
+          order.starts.data_ptr(),
           order.experts, _stream())
     return out
 
@@ -2137,7 +2275,8 @@ def moe_grouped_fits(K: int) -> bool:
 
 
 def moe_grouped(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated: bool,
-                limit: float = 0.0, alpha: float = 0.0, by_token: bool = False) -> torch.Tensor:
+                limit: float = 0.0, alpha: float = 0.0, by_token: bool = False,
+                shift: float = 1.0) -> torch.Tensor:
     """For every expert, its sorted rows of `x` times its matrix in `w` ([E, N, K],
     or [E, 2N, K] gate rows then up rows when `gated`, which also applies the
     activation); float32 out [pairs, N]. `by_token`: `x` holds the tokens' rows
@@ -2150,7 +2289,7 @@ def moe_grouped(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated: boo
     want = w.dtype if gated else torch.float32
     _call("fb_moe_grouped", 1 if gated else 0, _dev(x, "x", want), x.stride(0), _dev(w, "w"),
           code_of(w.dtype), order.starts.data_ptr(), out.data_ptr(), N, E, K, N, float(limit),
-          float(alpha), sm_count(), order.pair_at.data_ptr() if by_token else 0, order.top,
+          float(alpha), float(shift), sm_count(), order.pair_at.data_ptr() if by_token else 0, order.top,
           order.pairs, _stream())
     return out
 
@@ -2166,7 +2305,8 @@ def moe_grouped_mma_fits(x: torch.Tensor, *ks: int) -> bool:
 
 
 def moe_grouped_mma(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated: bool,
-                    limit: float = 0.0, alpha: float = 0.0, by_token: bool = False) -> torch.Tensor:
+                    limit: float = 0.0, alpha: float = 0.0, by_token: bool = False,
+                    shift: float = 1.0) -> torch.Tensor:
     """`moe_grouped` on the tensor cores (bfloat16 in; the gated product gives the
     activations in bfloat16, the other one float32)."""
     E, rows, K = w.shape
@@ -2177,14 +2317,16 @@ def moe_grouped_mma(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated:
         return out
     _call("fb_moe_grouped_mma", 1 if gated else 0, _dev(x, "x", torch.bfloat16), x.stride(0),
           _dev(w, "w", torch.bfloat16), order.starts.data_ptr(), out.data_ptr(), N, E, K, N,
-          float(limit), float(alpha), order.pair_at.data_ptr() if by_token else 0, order.top,
-          _stream())
+          float(limit), float(alpha), float(shift),
+          order.pair_at.data_ptr() if by_token else 0, order.top, _stream())
     return out
 
 
 def moe_combine(y: torch.Tensor, order: ExpertOrder, weights: torch.Tensor,
-                out: torch.Tensor) -> torch.Tensor:
+                out: torch.Tensor, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = the weighted sum of token t's experts' rows of `y` (+ addend[t])."""
     _call("fb_moe_combine", _dev(y, "y", torch.float32), order.place.data_ptr(),
           _dev(weights, "weights", torch.float32), order.top, _dev(out, "out", torch.float32),
-          order.T, out.shape[1], _stream())
+          order.T, out.shape[1], 0 if addend is None else _dev(addend, "addend", torch.float32),
+          _stream())
     return out

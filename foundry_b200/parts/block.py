@@ -98,13 +98,28 @@ class SandwichNormBlock(Part):
     leaves as an `ops.NormedDelta` (its post-norm still to be applied) and the
     norm that runs next makes `x += post(y)` and its own normalisation in one
     pass over the row, so the block, like `pre_norm_residual`, returns its last
-    output un-added. The residual stream and all statistics are 32-bit."""
+    output un-added. The residual stream and all statistics are 32-bit.
+
+    With `depth` = n > 0 the block is the n-th of `depth_total` whose results are
+    kept, and what leaves it is a weighted sum over all streams so far:
+
+        X_n = the block's result;  x <- sum_j w[j] X_j, j = 0 .. n
+
+    X_0 being the stream as the embedding left it and w the tensor
+    `<prefix>.<depth_name>` of n + 1 numbers. The sum is work of the norm that
+    runs next, too: the block's output leaves as an `ops.DepthMix`."""
     replay_safe = True
 
-    def __init__(self, layer: LayerSpec, *, dtype: torch.dtype, device: torch.device):
+    def __init__(self, layer: LayerSpec, depth: int = 0, depth_total: int = 0,
+                 depth_name: str = "dwa", *, dtype: torch.dtype, device: torch.device):
         ctx = dict(dtype=dtype, device=device)
         if layer.mixer_post_norm is None:
             raise ValueError("sandwich_norm_residual needs a norm behind the mixer")
+        if depth < 0 or (depth > 0 and depth > depth_total):
+            raise ValueError(f"block {depth} of {depth_total} kept streams")
+        self.depth, self.depth_total, self.depth_name = int(depth), int(depth_total), depth_name
+        self.needs_embedding_output = self.depth > 0
+        self.depth_weights = None
         self.prefix = layer.prefix
         self.names = dict(layer.names)
         self.mixer = MIXERS.build(layer.mixer, **ctx)
@@ -136,11 +151,16 @@ class SandwichNormBlock(Part):
         out: Dict[str, ExpectedTensor] = {}
         for part, name in self._named():
             out.update(part.expected_tensors(name))
+        if self.depth:
+            out[f"{self.prefix}.{self.depth_name}"] = ExpectedTensor((self.depth + 1,))
         return out
 
     def load(self, prefix: str, fetch: Fetch) -> None:
         for part, name in self._named():
             part.load(name, fetch)
+        if self.depth:
+            self.depth_weights = fetch(f"{self.prefix}.{self.depth_name}").to(
+                torch.float32).contiguous()
 
     def cache_request(self):
         return self.mixer.cache_request()
@@ -154,10 +174,25 @@ class SandwichNormBlock(Part):
         normed = self.mixer_norm.add_norm(resid, delta)
         mixed = _as_rows(self.mixer.forward(ctx, normed, cache))
         pending = self.mixer_post_norm.pending(mixed)
-        if self.feed_forward is None:
+        if self.feed_forward is not None:
+            normed = self.feed_forward_norm.add_norm(resid, pending)
+            pending = self.feed_forward_post_norm.pending(
+                _as_rows(self.feed_forward.forward(ctx, normed)))
+        if not self.depth:
             return pending
-        normed = self.feed_forward_norm.add_norm(resid, pending)
-        return self.feed_forward_post_norm.pending(_as_rows(self.feed_forward.forward(ctx, normed)))
+        from ..kernels import ops
+        kept = ctx.shared.get(KEPT_STREAMS)
+        if kept is None or kept.shape[0] < self.depth_total or kept.shape[1:] != resid.shape:
+            kept = ctx.shared[KEPT_STREAMS] = torch.empty(
+                (self.depth_total, *resid.shape), dtype=torch.float32, device=resid.device)
+        return ops.DepthMix(pending, ctx.shared[EMBEDDING_OUTPUT], kept, self.depth_weights,
+                            self.depth)
+
+
+# keys of `ctx.shared`: the stream as the embedding left it (the model puts it there for
+# blocks that say `needs_embedding_output`), and the blocks' kept results [depth, T, W]
+EMBEDDING_OUTPUT = "embedding_output"
+KEPT_STREAMS = "kept_streams"
 
 
 def _as_rows(y):

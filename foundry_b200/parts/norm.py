@@ -85,8 +85,14 @@ class LayerNorm(Part):
         return ops.NormedDelta(values, self.weight, self.bias, self.eps)
 
     def add_norm(self, resid: torch.Tensor, delta, out: Optional[torch.Tensor] = None):
-        """resid += delta (None, a tensor, split-K planes, or an `ops.NormedDelta`
-        whose norm is applied on the way); returns LN(resid) in the activation dtype."""
+        """resid += delta (None, a tensor, split-K planes, an `ops.NormedDelta` whose norm
+        is applied on the way, or an `ops.DepthMix`, which also replaces the stream by
+        its weighted sum); returns LN(resid) in the activation dtype."""
+        mix = None
+        if isinstance(delta, ops.DepthMix):  # the stream is a weighted sum over kept streams
+            mix, delta = delta, delta.pending
+            if delta is not None and delta.eps != self.eps:
+                mix, delta = None, mix.settle(resid)
         if isinstance(delta, ops.Planes):
             delta = delta.sum(torch.float32)
         if delta is not None and not isinstance(delta, ops.NormedDelta):
@@ -95,4 +101,4 @@ class LayerNorm(Part):
             delta = delta.settle(resid)
         if out is None:
             out = torch.empty(resid.shape, dtype=self.dtype, device=resid.device)
-        return ops.ln_add_ln(resid, delta, self.weight, self.bias, self.eps, out)
+        return ops.ln_add_ln(resid, delta, self.weight, self.bias, self.eps, out, mix=mix)

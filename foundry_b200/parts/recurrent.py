@@ -27,6 +27,17 @@
     o = (S + diag(u) k v^T)^T r;  S <- diag(w) S + k v^T
     out = Wo [ o / rms(o per head) * norm * gate ]          (norm [heads * dim])
 
+`state_space_duality`: the Mamba-2 layer.
+
+    W_in h = [z: inner | x: inner | B: groups x state | C: groups x state | dt: heads],
+    inner = heads x vdim;  x, B, C together pass a causal convolution per channel (`taps`
+    weights and a bias, the newest input under the last weight, zeros in front of the
+    sequence) and SiLU;  dt <- softplus(dt + dt_bias), no clamp;  per head a (group
+    a // (heads / groups)):
+    S <- exp(-exp(A_log[a]) dt) S + dt B x^T   (S [state, vdim]);  y = S^T C + D[a] x
+    out = Wo [ rms_parts(y * silu(z)) * norm ]   (the gate first; the row normalised in
+    `norm_groups` equal parts, each by its own root mean square)
+
 The state S is float32 and, with the inputs that the next step needs from this
 one (the convolution's last taps - 1 inputs; the last h), one float32 row per
 sequence in the cache's state storage. Decays, step sizes, gates, unit norms
@@ -239,4 +250,89 @@ class WkvTimeMix(Part):
         ops.state_scan(ctx, ops.SCAN_WKV, r, k, v, decay, state, "S", o, H, 1, d, d, bonus=self.u)
         y = torch.empty((T, H * d), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(o, self.norm, True, g, "silu", self.eps, y, H, d)
+        return product_f32(y, self.o)
+
+
+@register_mixer("state_space_duality")
+class StateSpaceDuality(Part):
+    """The Mamba-2 layer (see the module's notes). Tensor names under the prefix:
+    `in`, `conv`, `conv.b`, `dt_bias`, `A_log`, `D`, `norm`, `o`."""
+    replay_safe = True
+
+    def __init__(self, width: int, heads: int, vdim: int, state: int, groups: int, taps: int,
+                 eps: float, norm_groups: int = 1, *, dtype: torch.dtype, device: torch.device):
+        if groups <= 0 or heads % groups:
+            raise ValueError(f"{heads} heads are not a multiple of {groups} groups")
+        if state > 512:
+            raise ValueError(f"a state of {state} rows a head: the recurrence kernel holds at most 512")
+        inner = heads * vdim
+        if norm_groups <= 0 or inner % norm_groups:
+            raise ValueError(f"{inner} inner channels are not a multiple of {norm_groups} norm groups")
+        self.width, self.heads, self.vdim, self.state, self.groups = width, heads, vdim, state, groups
+        self.taps, self.eps, self.norm_groups = int(taps), float(eps), int(norm_groups)
+        self.inner = inner
+        self.channels = inner + 2 * groups * state   # what passes the convolution
+        self.rows_in = 2 * inner + 2 * groups * state + heads
+        self.dtype, self.device = dtype, device
+        self.fields = [("tail", (self.taps - 1) * self.channels), ("S", heads * state * vdim)]
+
+    def _shapes(self):
+        return {"in": (self.rows_in, self.width), "conv": (self.channels, self.taps),
+                "conv.b": (self.channels,), "dt_bias": (self.heads,), "A_log": (self.heads,),
+                "D": (self.heads,), "norm": (self.inner,), "o": (self.width, self.inner)}
+
+    def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
+        return {f"{prefix}.{n}": ExpectedTensor(s) for n, s in self._shapes().items()}
+
+    def load(self, prefix: str, fetch: Fetch) -> None:
+        f = lambda n: fetch(f"{prefix}.{n}")
+        self.w_in, self.o = f("in").contiguous(), f("o").contiguous()
+        self.conv, self.conv_bias = _f32(f("conv")), _f32(f("conv.b"))
+        self.dt_bias, self.A_log, self.skip = _f32(f("dt_bias")), _f32(f("A_log")), _f32(f("D"))
+        self.norm = _f32(f("norm"))
+
+    def cache_request(self) -> StateRequest:
+        return StateRequest((max(1, sum(n for _, n in self.fields)),), torch.float32)
+
+    def first_weight(self):
+        return self.w_in
+
+    # the same three pieces as the attention beside which it may stand (parts/parallel.py)
+    def input_weight(self) -> torch.Tensor:
+        return self.w_in
+
+    def output_weight(self) -> torch.Tensor:
+        return self.o
+
+    @property
+    def inner_size(self) -> int:
+        return self.inner
+
+    def between(self, ctx, p: torch.Tensor, cache: StateView, out: torch.Tensor,
+                out_scale: float = 1.0) -> torch.Tensor:
+        """From the input projection `p` (float32 rows [z | x | B | C | dt]) to the gated,
+        normalised rows in `out` (rows may lie further apart), times `out_scale`."""
+        T = p.shape[0]
+        H, G, N, v, C, inner = self.heads, self.groups, self.state, self.vdim, self.channels, \
+            self.inner
+        f32 = dict(dtype=torch.float32, device=p.device)
+        state = ops.StateRows(cache.rows, self.fields)
+        xbc = torch.empty((T, C), **f32)
+        if not ops.conv_silu_unit(ctx, p[:, inner:], self.conv, state, "tail", xbc, C,
+                                  bias=self.conv_bias):
+            ops.state_tail_update(ctx, p[:, inner:], state, "tail", self.taps - 1, C)
+        decay, steps = torch.empty((T, H), **f32), torch.empty((T, H), **f32)
+        ops.decay_gate(p[:, inner + C:inner + C + H], 1, self.dt_bias, self.A_log, out=decay,
+                       steps=steps)
+        y = torch.empty((T, inner), **f32)
+        ops.state_scan(ctx, ops.SCAN_SSD, xbc[:, inner + G * N:], xbc[:, inner:], xbc, decay, state,
+                       "S", y, H, H // G, N, v, beta=steps, bonus=self.skip, decay_per_head=True)
+        ops.head_norm_gate(y, self.norm, True, p[:, :inner], "silu", self.eps, out,
+                           self.norm_groups, inner // self.norm_groups, gate_first=True,
+                           out_scale=out_scale)
+        return out
+
+    def forward(self, ctx, x, cache: StateView):
+        y = torch.empty((x.shape[0], self.inner), dtype=x.dtype, device=x.device)
+        self.between(ctx, product_f32(x, self.w_in), cache, y)
         return product_f32(y, self.o)
