@@ -69,7 +69,34 @@ def _vonulorn(layers, width, heads, kv_heads, dim, ff, vocab, kv_rank, q_rank, t
             "residual_mult": 0.7, "layers": stack}
 
 
+def _vikarax(layers, width, heads, kv_heads, dim, ff, vocab, chunk=1024, state=128, taps=4,
+             experts=16, top=2) -> Dict:
+    """A Vikarax stack of real layer sizes: every layer the two mixers side by side
+    (sigmoid attention inside chunks of `chunk` positions with half of each head
+    rotated; a Mamba-2 layer of as many heads of the same size, eight groups of
+    `state` rows), dense and routed feed-forwards alternating (an expert and the
+    shared expert a quarter as wide as the dense one, four groups of experts of
+    which two are kept)."""
+    stack = []
+    for i in range(layers):
+        mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                          "scale": dim ** -0.5, "mask": {"size": chunk},
+                          "rot": {"dims": dim // 2, "base": 10000.0}},
+                 "right": {"heads": heads, "vdim": dim, "state": state, "groups": kv_heads,
+                           "conv": taps, "norm_groups": kv_heads},
+                 "left_scale": 0.5, "right_scale": 0.5}
+        mlp = {"kind": "dense", "ff": ff} if i % 2 == 0 else \
+            {"kind": "moe", "expert": {"ff": ff // 4},
+             "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}},
+             "shared": {"ff": ff // 4}}
+        stack.append({"type": "parallel", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Vikarax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "logit_softcap": 30.0, "layers": stack}
+
+
 PRESETS: Dict[str, Dict] = {
+    "vikarax-1b-layers": _vikarax(6, 2048, 32, 8, 64, 8192, 32000),
+    "vikarax-3b-layers": _vikarax(6, 3072, 24, 8, 128, 8192, 32000),
     "vonulorn-1b-layers": _vonulorn(6, 2048, 32, 8, 64, 8192, 32000, 256, 768),
     "vonulorn-3b-layers": _vonulorn(6, 3072, 24, 8, 128, 8192, 32000, 512, 1536),
     # six layers of the 1B and 3B layer sizes, as Rupotar and as Llama, for side-by-side timing

@@ -62,8 +62,8 @@ __global__ void moe_route_kernel(const float* z, long long ld, const float* __re
     for (int c = 0; c < keep; ++c) {
       float best = -INFINITY;
       int at = 0x7fffffff;
-      for (int g = lane; g < groups; g += 32)
-        if (s_group[g] > best) { best = s_group[g]; at = g; }
+      for (int g = lane; g < groups; g += 32)  // (a group kept earlier is marked with INFINITY)
+        if (s_group[g] != INFINITY && s_group[g] > best) { best = s_group[g]; at = g; }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, o);

@@ -97,6 +97,10 @@ _SIGNATURES = {
                              c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_void_p, c_void_p,
                              c_ll, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
+    "fb_attention_sigmoid_mma": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_void_p, c_void_p,
+                                 c_ll, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_int, c_void_p],
     "fb_embed_sinusoid": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_void_p],
     "fb_concat_cast": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -2024,6 +2028,13 @@ def head_norm_rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor,
     return q_out
 
 
+# (key, value) sizes of the tensor-core prompt kernel; a prompt step in bfloat16 of such
+# sizes takes it, every other step the CUDA-core kernel
+SIGMOID_TC_SIZES = {(32, 32), (64, 64), (128, 128), (64, 128), (128, 64), (96, 64), (32, 64),
+                    (32, 128)}
+SIGMOID_ATTENTION_TC = _os.environ.get("FOUNDRY_B200_SIGMOID_ATTENTION_TC", "1") != "0"
+
+
 def attention_sigmoid(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache, v_cache,
                       H: int, G: int, dim: int, vdim: int, scale: float, chunk: int = 0,
                       head_bias: Optional[torch.Tensor] = None,
@@ -2037,6 +2048,19 @@ def attention_sigmoid(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cac
     _check_kv_pair(k_cache, v_cache, G, dim, vdim, q.dtype)
     if head_bias is not None and tuple(head_bias.shape) != (H,):
         raise KernelError(f"attention_sigmoid: {tuple(head_bias.shape)} biases for {H} heads")
+    if (SIGMOID_ATTENTION_TC and not ctx.is_decode and q.dtype == torch.bfloat16
+            and (dim, vdim) in SIGMOID_TC_SIZES):
+        _call("fb_attention_sigmoid_mma", _dev(q, "q", contiguous=False), _rows(q, "q"),
+              _dev(out, "out", q.dtype, contiguous=False), _rows(out, "out"),
+              _dev(ctx.cu_tokens, "cu_tokens", torch.int32), _dev(ctx.kv_lens, "kv_lens", torch.int32),
+              _dev(page_table, "page_table", torch.int32), page_table.shape[1],
+              k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
+              v_cache.stride(0), v_cache.stride(1),
+              0 if head_bias is None else _dev(head_bias, "head_bias", torch.float32),
+              0 if gate is None else _dev(gate, "gate", torch.float32, contiguous=False),
+              0 if gate is None else _rows(gate, "gate"), float(scale), float(out_scale),
+              int(chunk or 0), ctx.n_seqs, _query_blocks(ctx), H, G, dim, vdim, _stream())
+        return out
     _call("fb_attention_sigmoid", _dev(q, "q", contiguous=False), _rows(q, "q"),
           _dev(out, "out", q.dtype, contiguous=False), _rows(out, "out"), code_of(q.dtype),
           _dev(ctx.positions, "positions", torch.int32),

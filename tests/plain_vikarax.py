@@ -177,8 +177,29 @@ def route(mlp, scores):
     return sorted(allowed, key=lambda x: (-float(scores[x]), x))[:top]
 
 
-def routed_experts(mlp, w, p, h):
+def route_margin(mlp, scores):
+    """How far one token's choice is from another one: the gap between the last kept
+    group and the first dropped one, and between the last chosen expert and the first
+    allowed one that is not chosen; the smaller of the two (inf where nothing is dropped)."""
+    r = mlp["router"]
+    E, top = r["experts"], r["top"]
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    per = E // groups["count"]
+    of_group = [sum(sorted(scores[g * per:(g + 1) * per].tolist(), reverse=True)[:2])
+                for g in range(groups["count"])]
+    order = sorted(range(groups["count"]), key=lambda g: (-of_group[g], g))
+    keep = groups["keep"]
+    gap = of_group[order[keep - 1]] - of_group[order[keep]] if keep < len(order) else float("inf")
+    allowed = sorted((float(scores[x]) for x in range(E) if x // per in order[:keep]), reverse=True)
+    if top < len(allowed):
+        gap = min(gap, allowed[top - 1] - allowed[top])
+    return gap
+
+
+def routed_experts(mlp, w, p, h, margins=None):
     scores = sigmoid(h @ w[f"{p}.router"].T)
+    if margins is not None:
+        margins.append([route_margin(mlp, scores[t]) for t in range(h.shape[0])])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for x in route(mlp, scores[t]):
@@ -188,7 +209,7 @@ def routed_experts(mlp, w, p, h):
     return out
 
 
-def layer(cfg, w, i, x):
+def layer(cfg, w, i, x, margins=None):
     """The result of layer i (before the weighted sum over the streams)."""
     entry, p, eps = cfg["layers"][i], f"l{i}", cfg["norm"]["eps"]
     norm = lambda name, t: layer_norm(t, w[f"{p}.{name}"], w[f"{p}.{name}.b"], eps)
@@ -197,7 +218,7 @@ def layer(cfg, w, i, x):
     if mlp is not None:
         h = norm("norm2", x)
         y = dense_feed_forward(w, f"{p}.mlp", h) if mlp["kind"] == "dense" else \
-            routed_experts(mlp, w, f"{p}.mlp", h)
+            routed_experts(mlp, w, f"{p}.mlp", h, margins)
         x = x + norm("norm2b", y)
     return x
 
@@ -206,12 +227,13 @@ def depth_average(kept, weights):
     return sum(weights[j] * kept[j] for j in range(len(kept)))
 
 
-def forward(cfg, w, tokens, streams=None):
-    """Logits [T, vocab] of a whole sequence; `streams` collects what leaves each layer."""
+def forward(cfg, w, tokens, streams=None, margins=None):
+    """Logits [T, vocab] of a whole sequence; `streams` collects what leaves each layer,
+    `margins` the routers' margins (`route_margin`), a list per routed layer."""
     x = w["embed"][torch.as_tensor(tokens)]
     kept = [x]
     for i in range(len(cfg["layers"])):
-        kept.append(layer(cfg, w, i, x))
+        kept.append(layer(cfg, w, i, x, margins))
         x = depth_average(kept, w[f"l{i}.dwa"])
         if streams is not None:
             streams.append(x)

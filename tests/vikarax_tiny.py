@@ -66,6 +66,38 @@ CONFIGS = {
 }
 
 
+def mixer_shapes(p, m, W):
+    """The tensors of one parallel mixer under the prefix `p` (config entry `m`)."""
+    a, s = m["left"], m["right"]
+    H, G, d, e = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+    shapes = {f"{p}.left.q": (H * d, W), f"{p}.left.k": (G * d, W),
+              f"{p}.left.v": (G * e, W), f"{p}.left.q.norm": (d,),
+              f"{p}.left.k.norm": (d,), f"{p}.left.pb": (H,),
+              f"{p}.left.g": (H, W), f"{p}.left.o": (W, H * e)}
+    inner, GN = s["heads"] * s["vdim"], s["groups"] * s["state"]
+    shapes.update({f"{p}.right.in": (2 * inner + 2 * GN + s["heads"], W),
+                   f"{p}.right.conv": (inner + 2 * GN, s["conv"]),
+                   f"{p}.right.conv.b": (inner + 2 * GN,),
+                   f"{p}.right.dt_bias": (s["heads"],), f"{p}.right.A_log": (s["heads"],),
+                   f"{p}.right.D": (s["heads"],), f"{p}.right.norm": (inner,),
+                   f"{p}.right.o": (W, inner)})
+    return shapes
+
+
+def mlp_shapes(p, mlp, W):
+    if mlp["kind"] == "dense":
+        return {f"{p}.up": (mlp["ff"], W), f"{p}.down": (W, mlp["ff"])}
+    ff, E = mlp["expert"]["ff"], mlp["router"]["experts"]
+    shapes = {f"{p}.router": (E, W)}
+    names = [(f"e{x}", ff) for x in range(E)]
+    if mlp.get("shared"):
+        names.append(("shared", mlp["shared"]["ff"]))
+    for name, size in names:
+        shapes.update({f"{p}.{name}.gate": (size, W), f"{p}.{name}.up": (size, W),
+                       f"{p}.{name}.down": (W, size)})
+    return shapes
+
+
 def tensor_shapes(cfg):
     W, V = cfg["width"], cfg["vocab"]
     shapes = {"embed": (V, W), "head": (V, W), "final.norm": (W,), "final.norm.b": (W,)}
@@ -75,65 +107,49 @@ def tensor_shapes(cfg):
         for n in norms:
             shapes[f"{p}.{n}"] = shapes[f"{p}.{n}.b"] = (W,)
         shapes[f"{p}.dwa"] = (i + 2,)
-        a, s = layer["mixer"]["left"], layer["mixer"]["right"]
-        H, G, d, e = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
-        shapes.update({f"{p}.mix.left.q": (H * d, W), f"{p}.mix.left.k": (G * d, W),
-                       f"{p}.mix.left.v": (G * e, W), f"{p}.mix.left.q.norm": (d,),
-                       f"{p}.mix.left.k.norm": (d,), f"{p}.mix.left.pb": (H,),
-                       f"{p}.mix.left.g": (H, W), f"{p}.mix.left.o": (W, H * e)})
-        inner, GN = s["heads"] * s["vdim"], s["groups"] * s["state"]
-        shapes.update({f"{p}.mix.right.in": (2 * inner + 2 * GN + s["heads"], W),
-                       f"{p}.mix.right.conv": (inner + 2 * GN, s["conv"]),
-                       f"{p}.mix.right.conv.b": (inner + 2 * GN,),
-                       f"{p}.mix.right.dt_bias": (s["heads"],), f"{p}.mix.right.A_log": (s["heads"],),
-                       f"{p}.mix.right.D": (s["heads"],), f"{p}.mix.right.norm": (inner,),
-                       f"{p}.mix.right.o": (W, inner)})
-        mlp = layer["mlp"]
-        if mlp and mlp["kind"] == "dense":
-            shapes.update({f"{p}.mlp.up": (mlp["ff"], W), f"{p}.mlp.down": (W, mlp["ff"])})
-        elif mlp:
-            ff, E = mlp["expert"]["ff"], mlp["router"]["experts"]
-            shapes[f"{p}.mlp.router"] = (E, W)
-            names = [(f"e{x}", ff) for x in range(E)]
-            if mlp.get("shared"):
-                names.append(("shared", mlp["shared"]["ff"]))
-            for name, size in names:
-                shapes.update({f"{p}.mlp.{name}.gate": (size, W), f"{p}.mlp.{name}.up": (size, W),
-                               f"{p}.mlp.{name}.down": (W, size)})
+        shapes.update(mixer_shapes(f"{p}.mix", layer["mixer"], W))
+        if layer["mlp"]:
+            shapes.update(mlp_shapes(f"{p}.mlp", layer["mlp"], W))
     return shapes
 
 
+def draw(key, shape, gen):
+    """One bfloat16-representable float32 tensor. Matrices are wide enough that a
+    wrong key, state or expert moves the logits; norm weights lie around one; step
+    sizes and decays in ranges where a state lasts for a few dozen tokens; the
+    streams' weights around one half, of either sign."""
+    leaf = key.split(".")[-1]
+    r = torch.randn(shape, generator=gen)
+    if key.endswith(".b") and ("norm" in key or "conv" in key) or leaf in ("pb",):
+        t = 0.3 * r
+    elif leaf == "dt_bias":
+        t = -1.0 + 0.5 * r
+    elif leaf in ("norm", "norm1", "norm1b", "norm2", "norm2b") and len(shape) == 1:
+        t = 1.0 + 0.2 * r
+    elif leaf == "A_log":
+        t = -1.0 + 0.5 * r
+    elif leaf == "D":
+        t = 1.0 + 0.3 * r
+    elif leaf == "conv":
+        t = 0.5 * r
+    elif leaf == "dwa":
+        t = 0.5 + 0.4 * r
+    elif leaf == "embed":
+        t = 0.5 * r
+    else:
+        t = r / (shape[-1] ** 0.5) * 1.5
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
 def random_weights(name, seed=0):
-    """bfloat16-representable float32 tensors by file name. Matrices are wide
-    enough that a wrong key, state or expert moves the logits; norm weights lie
-    around one; step sizes and decays in ranges where a state lasts for a few
-    dozen tokens; the streams' weights around one half, of either sign."""
-    cfg = CONFIGS[name]
+    """Every tensor of the configuration `name`, by file name."""
     gen = torch.Generator().manual_seed(seed)
-    out = {}
-    for key, shape in tensor_shapes(cfg).items():
-        leaf = key.split(".")[-1]
-        r = torch.randn(shape, generator=gen)
-        if key.endswith(".b") and ("norm" in key or "conv" in key) or leaf in ("pb",):
-            t = 0.3 * r
-        elif leaf == "dt_bias":
-            t = -1.0 + 0.5 * r
-        elif leaf in ("norm", "norm1", "norm1b", "norm2", "norm2b") and len(shape) == 1:
-            t = 1.0 + 0.2 * r
-        elif leaf == "A_log":
-            t = -1.0 + 0.5 * r
-        elif leaf == "D":
-            t = 1.0 + 0.3 * r
-        elif leaf == "conv":
-            t = 0.5 * r
-        elif leaf == "dwa":
-            t = 0.5 + 0.4 * r
-        elif leaf == "embed":
-            t = 0.5 * r
-        else:
-            t = r / (shape[-1] ** 0.5) * 1.5
-        out[key] = t.to(torch.bfloat16).to(torch.float32)
-    return out
+    return {key: draw(key, shape, gen) for key, shape in tensor_shapes(CONFIGS[name]).items()}
+
+
+def random_tensors(shapes, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    return {key: draw(key, shape, gen) for key, shape in shapes.items()}
 
 
 def write_folder(folder, name, seed=0):
