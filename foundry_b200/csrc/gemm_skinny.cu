@@ -429,7 +429,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
       }
     }
   } else {
-    if (epilogue == 0) {
+    if (epilogue == 0 || epilogue == 5) {
       for (int idx = threadIdx.x; idx < 16 * T; idx += WARPS * 32) {
         const int row = idx & 15, tok = idx >> 4;
         if (n0 + row >= N) continue;
@@ -437,6 +437,10 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
 #pragma unroll
         for (int wi = 0; wi < WARPS; ++wi) v += red[wi][row][tok];
         v *= row_scale(tok);
+        if (epilogue == 5) {  // the square of relu, of the 32-bit sum
+          v = fmaxf(v, 0.f);
+          v *= v;
+        }
         const size_t o = (size_t)tok * ldo + n0 + row;
         if (out_f32) out_f[o] = v;
         else out_h[o] = __float2bfloat16_rn(v);
@@ -568,7 +572,9 @@ FB_API int fb_gemm_skinny(const void* x, long long ldx, const void* w, long long
                           int scale_count, int scale_stride, int scale_dim, float scale_eps,
                           cudaStream_t stream) {
   // epilogue 4: as 1 with the tanh form of GELU on the gate
-  FB_REQUIRE(epilogue == 0 || epilogue == 1 || epilogue == 4, "gemm_skinny: epilogue %d", epilogue);
+  // epilogue 5: as 0 with out = max(out, 0)^2
+  FB_REQUIRE(epilogue == 0 || epilogue == 1 || epilogue == 4 || epilogue == 5,
+             "gemm_skinny: epilogue %d", epilogue);
   const RowScale scale{scale_ss, scale_count, scale_stride,
                        scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps};
   return launch_skinny(x, ldx, w, ldw, out, ldo, out_f32, T, N, K, epilogue, next, next_bytes,

@@ -544,7 +544,7 @@ __global__ void moe_combine_kernel(const float* y, const int* place, const float
   fb_pdl_launch();
   fb_pdl_wait();
   const size_t t = blockIdx.x;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < W; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
     for (int c = 0; c < top; ++c) {
       const int at = place[t * top + c];
@@ -663,6 +663,9 @@ FB_API int fb_moe_combine(const float* y, const int* place, const float* weights
                           float* out, int T, int W, const float* addend, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && W > 0 && top > 0, "moe_combine: bad sizes");
   if (T == 0) return 0;
-  fb_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, y, place, weights, top, out, W, addend);
+  const int want = (W + 255) / 256;  // few tokens: a row's columns go to several blocks
+  const int parts = T <= 256 ? (want < 32 ? want : 32) : 1;
+  fb_launch(moe_combine_kernel, dim3(T, parts), dim3(256), 0, stream, y, place, weights, top, out, W,
+            addend);
   return fb_check_launch("moe_combine");
 }

@@ -137,6 +137,39 @@ __global__ void conv_silu_unit_kernel(const float* x, long long ld, const float*
   for (int c = threadIdx.x; c < C; c += blockDim.x) out[(size_t)t * C + c] = y[c];
 }
 
+// The same without unit heads: nothing ties a token's channels together, so they are
+// spread over blockIdx.y and written as they are made.
+__global__ void conv_silu_kernel(const float* x, long long ld, const float* __restrict__ w,
+                                 const float* __restrict__ bias, int taps, float* state,
+                                 long long state_stride, long long tail_offset,
+                                 float* __restrict__ out, int C, const int* __restrict__ seq_of_token,
+                                 const int* __restrict__ cu_tokens, const int* __restrict__ slots,
+                                 int single) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int seq = seq_of_token[t];
+  if (seq < 0) {
+    out[(size_t)t * C + c] = 0.f;
+    return;
+  }
+  const int start = cu_tokens[seq];
+  const int n_tail = taps - 1;
+  float* tail = state + (long long)slots[seq] * state_stride + tail_offset;
+  float acc = 0.f;
+  for (int a = 0; a < taps; ++a) {
+    const int idx = t - (taps - 1 - a) - start;  // row of the step, negative: the tail
+    const float v = idx >= 0 ? __ldcg(x + (size_t)(start + idx) * ld + c)
+                             : __ldcg(tail + (size_t)(n_tail + idx) * C + c);
+    acc = fmaf(w[(size_t)c * taps + a], v, acc);
+    if (single && a > 0) tail[(size_t)(a - 1) * C + c] = v;  // as in the kernel above
+  }
+  if (bias != nullptr) acc += bias[c];
+  out[(size_t)t * C + c] = acc * sigmoidf_(acc);
+}
+
 // -------------------------------------------------------------------- decays
 // mode 0: out <- exp(-exp(A[head]) * softplus(x + bias[c]))   (c = head * per_head + channel;
 //         per_head = 1: one decay a head)
@@ -376,6 +409,8 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc) {
 // out = y / sqrt(mean(y^2) + eps) * w with y = o * act(gate). A "head" is any equal part
 // of the row that is normalised by itself. Output rows lie `out_ld` elements apart and
 // are multiplied by `out_scale` before they are rounded.
+constexpr int HG_HOLD = 8;  // elements of a head a lane can hold (heads of up to 256)
+
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* o, const float* __restrict__ w, int w_stride,
                                       const float* gate, long long gate_ld, int act, float eps,
@@ -385,8 +420,39 @@ __global__ void head_norm_gate_kernel(const float* o, const float* __restrict__ 
   fb_pdl_wait();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int h = warp; h < H; h += nwarps) {
+  // a warp a head; the heads of a token are spread over blockIdx.y
+  for (int h = blockIdx.y * nwarps + warp; h < H; h += gridDim.y * nwarps) {
     const float* row = o + ((size_t)t * H + h) * vdim;
+    if (vdim <= 32 * HG_HOLD) {
+      // a lane holds its elements: every load of the head is on its way before the first
+      // is used, and nothing is read twice
+      float v[HG_HOLD], ga[HG_HOLD], wv[HG_HOLD];
+#pragma unroll
+      for (int i = 0; i < HG_HOLD; ++i) {
+        const int d = lane + 32 * i;
+        const bool in = d < vdim;
+        v[i] = in ? __ldcg(row + d) : 0.f;
+        ga[i] = in ? __ldcg(gate + (size_t)t * gate_ld + (size_t)h * vdim + d) : 0.f;
+        wv[i] = in ? w[(size_t)h * w_stride + d] : 0.f;
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < HG_HOLD; ++i) {
+        ga[i] = act == 0 ? sigmoidf_(ga[i]) : ga[i] * sigmoidf_(ga[i]);
+        if (gate_first) v[i] *= ga[i];
+        ss += v[i] * v[i];
+      }
+      const float r = 1.0f / sqrtf(fb_warp_sum(ss) / (float)vdim + eps);
+#pragma unroll
+      for (int i = 0; i < HG_HOLD; ++i) {
+        const int d = lane + 32 * i;
+        // (gate first: v already carries the gate)
+        if (d < vdim)
+          out[(size_t)t * out_ld + (size_t)h * vdim + d] =
+              fb_from_float<T>(v[i] * r * wv[i] * (gate_first ? 1.0f : ga[i]) * out_scale);
+      }
+      continue;
+    }
     float ss = 0.f;
     for (int d = lane; d < vdim; d += 32) {
       float v = __ldcg(row + d);
@@ -413,7 +479,7 @@ __global__ void unary_cast_kernel(const float* in, long long ld, T* __restrict__
   fb_pdl_launch();
   fb_pdl_wait();
   const size_t t = blockIdx.x;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
     const float v = __ldcg(in + t * ld + i);
     const float r = fmaxf(v, 0.f);
     out[t * n + i] = fb_from_float<T>(act == 1 ? tanhf(v) : act == 2 ? r * r : v);
@@ -453,8 +519,14 @@ FB_API int fb_conv_silu_unit(const float* x, long long ld, const float* w, const
   FB_REQUIRE(T >= 0 && C > 0 && taps >= 1 && ld >= C, "conv_silu_unit: bad sizes");
   FB_REQUIRE(n_unit >= 0 && (long long)n_unit * dim <= C && n_scaled <= n_unit,
              "conv_silu_unit: %d unit heads of %d exceed %d channels", n_unit, dim, C);
-  FB_REQUIRE((size_t)C * 4 <= 200 * 1024, "conv_silu_unit: %d channels do not fit shared memory", C);
+  FB_REQUIRE(n_unit == 0 || (size_t)C * 4 <= 200 * 1024,
+             "conv_silu_unit: %d channels do not fit shared memory", C);
   if (T == 0) return 0;
+  if (n_unit == 0) {
+    fb_launch(conv_silu_kernel, dim3(T, (C + 255) / 256), dim3(256), 0, stream, x, ld, w, bias, taps,
+              state, state_stride, tail_offset, out, C, seq_of_token, cu_tokens, slots, single);
+    return fb_check_launch("conv_silu");
+  }
   const size_t smem = (size_t)C * 4;
   static bool seen[64];
   if (smem > 48 * 1024 && fb_first_use_on_device(seen))
@@ -576,7 +648,9 @@ FB_API int fb_head_norm_gate(const float* o, const float* w, int w_stride, const
   FB_REQUIRE(out_ld >= (long long)H * vdim, "head_norm_gate: output rows of %lld are too short", out_ld);
   FB_REQUIRE(T >= 0 && H > 0 && vdim > 0 && (act == 0 || act == 1), "head_norm_gate: bad sizes");
   if (T == 0) return 0;
-  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(head_norm_gate_kernel<E>, dim3(T), dim3(256), 0, stream,
+  // few tokens: a token's heads go to several blocks, so that their loads run side by side
+  const int parts = T <= 256 ? (H + 7) / 8 : 1;
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(head_norm_gate_kernel<E>, dim3(T, parts), dim3(256), 0, stream,
       o, w, w_stride, gate, gate_ld, act, eps, (E*)out, out_ld, out_scale, H, vdim, gate_first)));
   return fb_check_launch("head_norm_gate");
 }
@@ -585,7 +659,9 @@ FB_API int fb_unary_cast(const float* in, long long ld, void* out, int dtype, in
                          cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && n > 0 && ld >= n, "unary_cast: bad sizes");
   if (T == 0) return 0;
-  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(unary_cast_kernel<E>, dim3(T), dim3(128), 0, stream, in,
+  const int want = (n + 511) / 512;  // two elements a thread, unless the rows alone fill the device
+  const int parts = T >= 1024 ? (want < 4 ? want : 4) : (want < 64 ? want : 64);
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(unary_cast_kernel<E>, dim3(T, parts), dim3(256), 0, stream, in,
       ld, (E*)out, n, act)));
   return fb_check_launch("unary_cast");
 }

@@ -97,6 +97,12 @@ _SIGNATURES = {
                              c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_void_p, c_void_p,
                              c_ll, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
+    # q, ld, out, ld, dtype, partial, positions, seq_of_token, page_table, max_pages, k, v,
+    # four strides, head_bias, gate, gate_ld, scale, out_scale, chunk, span, runs, T, H, G, dim, vdim
+    "fb_attention_sigmoid_group": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll,
+                                   c_void_p, c_void_p, c_ll, c_float, c_float, c_int, c_int, c_int,
+                                   c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_attention_sigmoid_mma": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_void_p, c_void_p,
                                  c_ll, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -763,7 +769,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
                 then_reads: Optional[torch.Tensor] = None, ksplit: int = 1,
                 warps: int = 0) -> torch.Tensor:
     """Up to 16 token rows: the weight-streaming kernel (csrc/gemm_skinny.cu).
-    epilogue 1: `w` rows are (gate, up) pairs and out is [M, N/2] = SiLU(gate)*up.
+    epilogue 1: `w` rows are (gate, up) pairs and out is [M, N/2] = SiLU(gate)*up
+    (4: the tanh form of GELU instead); epilogue 5: out = max(x w^T, 0)^2.
     `then_reads`: the weights the step streams after this product; the kernel's
     blocks ask for their start to be brought into L2 as they finish.
     `ksplit` > 1: K is shared by that many CTAs per row group and `out` is
@@ -774,7 +781,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     N = w.shape[0]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_skinny takes bfloat16 operands")
-    want = (M, N // 2) if epilogue else (M, N)
+    want = (M, N // 2) if epilogue in (1, 4) else (M, N)
     if ksplit > 1:
         want = (ksplit, *want)
         if out.dtype != torch.float32 or not out.is_contiguous():
@@ -1369,6 +1376,34 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
     else:
         gemm_tc(x, w_pairs, out, out.stride(0), 1, 128, epilogue=epilogue, constant_operand=2)
     return out
+
+
+UNARY_EPILOGUE = {"relu2": 5}
+
+
+def gemm_bf16_unary(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: str,
+                    then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = act(x @ w^T), the activation taken of the 32-bit sums. Few rows: in the
+    epilogue of the weight-streaming product; otherwise the product leaves float32 rows and
+    one pass over them applies the activation and rounds."""
+    M, K = x.shape
+    N = w.shape[0]
+    if out.shape != (M, N) or out.stride(1) != 1:
+        raise KernelError("gemm_bf16_unary: out must be [M, N] with contiguous rows")
+    if M == 0:
+        return out
+    inner = x.values if isinstance(x, RowScaled) else x
+    if (0 < M <= SKINNY_ROWS and inner.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and out.dtype == torch.bfloat16 and _tc_usable(inner, w, out)):
+        return gemm_skinny(x, w, out, epilogue=UNARY_EPILOGUE[act], then_reads=then_reads,
+                           warps=skinny_plan(N, K, False)[1])
+    raw = torch.empty((M, N), dtype=torch.float32, device=out.device)
+    x = plain(x)
+    if x.dtype == torch.float32:
+        gemm_simt(x, w, raw)
+    else:
+        gemm_bf16(x, w, raw)
+    return unary_cast(raw, out, act)
 
 
 FAST_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention kernels
@@ -2033,6 +2068,10 @@ def head_norm_rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor,
 SIGMOID_TC_SIZES = {(32, 32), (64, 64), (128, 128), (64, 128), (128, 64), (96, 64), (32, 64),
                     (32, 128)}
 SIGMOID_ATTENTION_TC = _os.environ.get("FOUNDRY_B200_SIGMOID_ATTENTION_TC", "1") != "0"
+# Single-token steps: the kernel in which a key head's query heads share the walk over the
+# keys ("0": the block-per-head kernel everywhere), and the keys a run of it holds.
+SIGMOID_ATTENTION_GROUPED = _os.environ.get("FOUNDRY_B200_SIGMOID_ATTENTION_GROUPED", "1") != "0"
+SIGMOID_RUN_KEYS = 1024
 
 
 def attention_sigmoid(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache, v_cache,
@@ -2060,6 +2099,26 @@ def attention_sigmoid(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cac
               0 if gate is None else _dev(gate, "gate", torch.float32, contiguous=False),
               0 if gate is None else _rows(gate, "gate"), float(scale), float(out_scale),
               int(chunk or 0), ctx.n_seqs, _query_blocks(ctx), H, G, dim, vdim, _stream())
+        return out
+    if SIGMOID_ATTENTION_GROUPED and ctx.max_q_len == 1:
+        # few tokens with many keys each: the heads of a key head share one walk, and a
+        # long range is cut into runs whose shares are added in run order
+        reach = min(int(chunk), ctx.max_kv_len) if chunk else ctx.max_kv_len
+        runs = max(1, -(-reach // SIGMOID_RUN_KEYS))
+        partial = (torch.empty((runs, T, H, vdim), dtype=torch.float32, device=q.device)
+                   if runs > 1 else None)
+        _call("fb_attention_sigmoid_group", _dev(q, "q", contiguous=False), _rows(q, "q"),
+              _dev(out, "out", q.dtype, contiguous=False), _rows(out, "out"), code_of(q.dtype),
+              0 if partial is None else partial.data_ptr(),
+              _dev(ctx.positions, "positions", torch.int32),
+              _dev(ctx.seq_of_token, "seq_of_token", torch.int32),
+              _dev(page_table, "page_table", torch.int32), page_table.shape[1],
+              k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
+              v_cache.stride(0), v_cache.stride(1),
+              0 if head_bias is None else _dev(head_bias, "head_bias", torch.float32),
+              0 if gate is None else _dev(gate, "gate", torch.float32, contiguous=False),
+              0 if gate is None else _rows(gate, "gate"), float(scale), float(out_scale),
+              int(chunk or 0), SIGMOID_RUN_KEYS, runs, T, H, G, dim, vdim, _stream())
         return out
     _call("fb_attention_sigmoid", _dev(q, "q", contiguous=False), _rows(q, "q"),
           _dev(out, "out", q.dtype, contiguous=False), _rows(out, "out"), code_of(q.dtype),

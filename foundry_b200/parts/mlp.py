@@ -107,10 +107,8 @@ class DenseMLP(Part):
 
     def forward(self, ctx, x):
         x = ops.plain(x)
-        raw = torch.empty((x.shape[0], self.intermediate_size), dtype=torch.float32,
-                          device=x.device)
-        raw = matmul_nt(x, self.up.weight, raw)
         hidden = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.unary_cast(raw, hidden, self.activation)
+        ops.gemm_bf16_unary(x, self.up.weight, hidden, self.activation,
+                            then_reads=self.down.weight)
         return self.down.forward(hidden, allow_planes=True,
                                  then_reads=getattr(ctx, "reads_after_part", None))

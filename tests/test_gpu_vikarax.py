@@ -349,6 +349,51 @@ def test_one_key_that_stands_out_on_both_sides_of_every_edge(sizes, chunk, dtype
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("chunk", [None, 650, 400])
+def test_single_tokens_whose_keys_fill_several_runs(chunk, dtype, monkeypatch):
+    """The single-token kernel cuts a long range of keys into runs (here of 256 keys, so
+    that a few hundred tokens make several) and adds the runs' shares: six query heads on
+    one key head with random weights (two blocks a key head, the second partly filled),
+    the last tokens decoded alone, against the plain attention; then the crafted key in
+    the first run, on both sides of a border between runs, in the last run and just
+    outside the chunk. The tokens decoded alone behind 800 others begin a chunk of 400,
+    so that all runs of the grid but the first hold no key."""
+    from foundry_b200.kernels import ops
+    monkeypatch.setattr(ops, "SIGMOID_RUN_KEYS", 256)
+    left = {"heads": 6, "kv_heads": 1, "dim": 24, "vdim": 40, "scale": 0.3,
+            "rot": {"dims": 8, "base": 50.0}}
+    if chunk:
+        left["mask"] = {"size": chunk}
+    m = {"left": left, "left_scale": 1.0, "right_scale": 0.5,
+         "right": {"heads": 2, "vdim": 8, "state": 8, "groups": 1, "conv": 2, "norm_groups": 1}}
+    W, eps = 48, 1e-5
+    weights = tiny.random_tensors(tiny.mixer_shapes("a", m, W), seed=21)
+    part = mixer_part(m, W, eps, weights, dtype)
+    cache = new_cache(part, 2048, 2, dtype)
+    torch.manual_seed(22)
+    x = torch.randn(820, W).to(dtype).float()
+    want = plain.parallel_mixer(m, double(weights), "a", x.double(), eps)
+    got = run_mixer(part, cache, [x], [[300, 500] + [1] * 20], dtype)[0]
+    assert rel_error(got, want) < bound(dtype)
+
+    m, weights = crafted_attention(32, 64, 64, chunk, 2, 1)
+    part = mixer_part(m, 32, 1e-6, weights, dtype)
+    cache = new_cache(part, 2048, 2, dtype)
+    wd = double(weights)
+    query_at = 780
+    lo = (query_at // chunk) * chunk if chunk else 0
+    for marker_at in (lo, lo + 255, lo + 256, lo + 300, query_at - 1, query_at, lo - 1, 0):
+        if marker_at < 0 or marker_at > query_at:
+            continue
+        xm = marked_inputs(query_at, marker_at, 32)
+        wanted = plain.parallel_mixer(m, wd, "a", xm.double(), 1e-6)[-1]
+        assert (float(wanted.norm()) > 0.5) == (marker_at >= lo), (marker_at, float(wanted.norm()))
+        found = run_mixer(part, cache, [xm], [[query_at, 1]], dtype)[0][-1].double()
+        err = float((found - wanted).norm()) / max(float(wanted.norm()), 0.05)
+        assert err < bound(dtype, 5.0), (chunk, marker_at, err)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_state_and_tail_survive_every_cutting(dtype):
     """Decays close to one, so that the first tokens still weigh on the last: the state
     and the convolution's tail carried through portions of one and two tokens equal the
