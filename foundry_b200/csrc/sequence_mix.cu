@@ -409,9 +409,9 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanArgs a, int tc) {
 // out = y / sqrt(mean(y^2) + eps) * w with y = o * act(gate). A "head" is any equal part
 // of the row that is normalised by itself. Output rows lie `out_ld` elements apart and
 // are multiplied by `out_scale` before they are rounded.
-constexpr int HG_HOLD = 8;  // elements of a head a lane can hold (heads of up to 256)
-
-template <typename T>
+// HG_HOLD: elements of a head a lane holds (heads of up to 32 * HG_HOLD; 0: any size, the
+// head is read twice)
+template <typename T, int HG_HOLD>
 __global__ void head_norm_gate_kernel(const float* o, const float* __restrict__ w, int w_stride,
                                       const float* gate, long long gate_ld, int act, float eps,
                                       T* __restrict__ out, long long out_ld, float out_scale,
@@ -423,7 +423,7 @@ __global__ void head_norm_gate_kernel(const float* o, const float* __restrict__ 
   // a warp a head; the heads of a token are spread over blockIdx.y
   for (int h = blockIdx.y * nwarps + warp; h < H; h += gridDim.y * nwarps) {
     const float* row = o + ((size_t)t * H + h) * vdim;
-    if (vdim <= 32 * HG_HOLD) {
+    if constexpr (HG_HOLD > 0) {
       // a lane holds its elements: every load of the head is on its way before the first
       // is used, and nothing is read twice
       float v[HG_HOLD], ga[HG_HOLD], wv[HG_HOLD];
@@ -451,8 +451,7 @@ __global__ void head_norm_gate_kernel(const float* o, const float* __restrict__ 
           out[(size_t)t * out_ld + (size_t)h * vdim + d] =
               fb_from_float<T>(v[i] * r * wv[i] * (gate_first ? 1.0f : ga[i]) * out_scale);
       }
-      continue;
-    }
+    } else {
     float ss = 0.f;
     for (int d = lane; d < vdim; d += 32) {
       float v = __ldcg(row + d);
@@ -468,6 +467,7 @@ __global__ void head_norm_gate_kernel(const float* o, const float* __restrict__ 
       const float ga = act == 0 ? sigmoidf_(gz) : gz * sigmoidf_(gz);
       out[(size_t)t * out_ld + (size_t)h * vdim + d] =
           fb_from_float<T>(__ldcg(row + d) * r * w[(size_t)h * w_stride + d] * ga * out_scale);
+    }
     }
   }
 }
@@ -650,8 +650,17 @@ FB_API int fb_head_norm_gate(const float* o, const float* w, int w_stride, const
   if (T == 0) return 0;
   // few tokens: a token's heads go to several blocks, so that their loads run side by side
   const int parts = T <= 256 ? (H + 7) / 8 : 1;
-  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(head_norm_gate_kernel<E>, dim3(T, parts), dim3(256), 0, stream,
-      o, w, w_stride, gate, gate_ld, act, eps, (E*)out, out_ld, out_scale, H, vdim, gate_first)));
+#define FB_HEAD_NORM_GATE(E, HOLD)                                                             \
+  fb_launch(head_norm_gate_kernel<E, HOLD>, dim3(T, parts), dim3(256), 0, stream, o, w, w_stride, \
+            gate, gate_ld, act, eps, (E*)out, out_ld, out_scale, H, vdim, gate_first)
+  FB_DISPATCH_DTYPE(dtype, E, {
+    if (vdim <= 64) FB_HEAD_NORM_GATE(E, 2);
+    else if (vdim <= 128) FB_HEAD_NORM_GATE(E, 4);
+    else if (vdim <= 256) FB_HEAD_NORM_GATE(E, 8);
+    else if (vdim <= 512) FB_HEAD_NORM_GATE(E, 16);
+    else FB_HEAD_NORM_GATE(E, 0);
+  });
+#undef FB_HEAD_NORM_GATE
   return fb_check_launch("head_norm_gate");
 }
 

@@ -447,7 +447,7 @@ FB_API int fb_head_norm_rope_cache_write(const float* qkv, long long ld, void* q
   const int head_floats = dim > vdim ? dim : vdim;
   const size_t smem = (size_t)(rot + warps * head_floats) * 4;
   FB_REQUIRE(smem <= 48 * 1024, "head_norm_rope_cache_write: heads of %d do not fit", head_floats);
-  const int parts = (heads + warps - 1) / warps;  // a warp a head, a head once
+  const int parts = T <= 256 ? (heads + warps - 1) / warps : 1;  // few tokens: more blocks
   FB_DISPATCH_DTYPE(dtype, E, (fb_launch(head_norm_rope_cache_kernel<E>, dim3(T, parts), dim3(warps * 32),
       smem, stream, qkv, ld, (E*)q_out, wq, wk, eps, value_norm, freq, rot, positions,
       seq_of_token, page_table, max_pages, (E*)k_cache, (E*)v_cache, k_page, k_head, v_page,

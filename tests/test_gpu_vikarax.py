@@ -158,10 +158,10 @@ OTHER_SIZES = [
      "right": {"heads": 2, "vdim": 16, "state": 8, "groups": 1, "conv": 3, "norm_groups": 2},
      "left_scale": 1.0, "right_scale": 1.0},
     # a chunk longer than every sequence of the test
-    {"left": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 128, "scale": 0.1,
-              "mask": {"size": 4096}, "rot": {"dims": 32, "base": 10000.0}},
+    {"left": {"heads": 8, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 0.1,
+              "mask": {"size": 4096}, "rot": {"dims": 16, "base": 5000.0}},
      "right": {"heads": 4, "vdim": 64, "state": 64, "groups": 4, "conv": 4, "norm_groups": 1},
-     "left_scale": 0.6, "right_scale": 1.1},
+     "left_scale": 0.8, "right_scale": 1.25},
 ]
 
 
