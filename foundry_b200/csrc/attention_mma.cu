@@ -136,8 +136,10 @@ struct AttnParams {
   // (window == 0 or i - j < window or j < keep_first); scores lose
   // 2^(-steep (head + 1) / A) per token of distance (steep 0: no bias); with `sink`
   // the softmax's sum has one more term exp(0), which adds nothing to the output
+  // (`sink_logits`, float32 per query head: the term is exp(sink_logits[head]) instead)
   int window, keep_first, sink;
   float steep;
+  const float* sink_logits;
 };
 
 // --------------------------------------------------------------------- prefill
@@ -208,7 +210,10 @@ attn_prefill_kernel(const AttnParams p) {
 #pragma unroll
   for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  if (EXT && p.sink) { m[0] = m[1] = 0.f; l[0] = l[1] = 1.f; }  // the term of score 0
+  if (EXT && p.sink) {  // the sink's term starts the running maximum and sum
+    m[0] = m[1] = p.sink_logits != nullptr ? p.sink_logits[head] * LOG2E : 0.f;
+    l[0] = l[1] = 1.f;
+  }
   const int qpos_lo = pos0 + warp * 16 + g;  // position of row g; row g + 8 is 8 further
 
   int it = 0;
@@ -915,7 +920,7 @@ FB_API int fb_attention_prefill_masked(const void* q, long long q_stride, void* 
                                        long long page_stride, long long head_stride, int n_seqs,
                                        int q_blocks, int A, int Kh, int D, float scale, int window,
                                        int keep_first, int sink, float steep,
-                                       cudaStream_t stream) {
+                                       const float* sink_logits, cudaStream_t stream) {
   int rc = check_common("attention_prefill_masked", n_seqs, A, Kh, D, q_stride, out_stride, q,
                         k_cache, v_cache, page_stride, head_stride);
   if (rc) return rc;
@@ -928,7 +933,8 @@ FB_API int fb_attention_prefill_masked(const void* q, long long q_stride, void* 
   p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
   p.page_stride = page_stride; p.head_stride = head_stride;
   p.n_seqs = n_seqs; p.A = A; p.Kh = Kh; p.scale_log2 = scale * LOG2E; p.splits = 1;
-  p.window = window; p.keep_first = keep_first; p.sink = sink ? 1 : 0; p.steep = steep;
+  p.window = window; p.keep_first = keep_first; p.steep = steep;
+  p.sink = (sink || sink_logits != nullptr) ? 1 : 0; p.sink_logits = sink_logits;
   switch (D) {
     case 16: return launch_prefill<16, true>(p, q_blocks, stream);
     case 32: return launch_prefill<32, true>(p, q_blocks, stream);

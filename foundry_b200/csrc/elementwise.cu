@@ -442,6 +442,25 @@ FB_API int fb_sum_planes(const float* planes, int S, long long n, long long plan
   return fb_check_launch("sum_planes");
 }
 
+// a[i] += b[i] (float32): two parts' results that join the residual as one sum.
+namespace {
+__global__ void add_into_kernel(float* a, const float* b, long long n) {
+  fb_pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    a[i] += __ldcg(b + i);
+}
+}  // namespace
+
+FB_API int fb_add_into(float* a, const float* b, long long n, cudaStream_t stream) {
+  FB_REQUIRE(n >= 0, "add_into: bad size %lld", n);
+  if (n == 0) return 0;
+  const long long want = (n + 255) / 256;
+  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  fb_launch(add_into_kernel, dim3(blocks), dim3(256), 0, stream, a, b, n);
+  return fb_check_launch("add_into");
+}
+
 // ------------------------------------------------------------- cap on values
 // x <- cap * tanh(x / cap), in place, 32-bit (a soft cap on the logits).
 namespace {

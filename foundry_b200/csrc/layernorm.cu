@@ -54,7 +54,7 @@ __device__ __forceinline__ void depth_mix_row(const DepthMix& m, float* row, flo
 
 template <typename TY, typename TO>
 __global__ void ln_add_ln_kernel(const TY* y, const float* __restrict__ w1,
-                                 const float* __restrict__ b1, float* resid,
+                                 const float* __restrict__ b1, float y_scale, float* resid,
                                  const float* __restrict__ w2, const float* __restrict__ b2,
                                  TO* __restrict__ out, int W, float eps, float inv_w,
                                  DepthMix mix) {
@@ -64,10 +64,10 @@ __global__ void ln_add_ln_kernel(const TY* y, const float* __restrict__ w1,
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * W;
   float* x = resid + base;
-  if (y != nullptr && w1 == nullptr) {  // a plain sum: y joins the residual as it is
+  if (y != nullptr && w1 == nullptr) {  // a plain sum: y joins the residual times a constant
     const TY* yr = y + base;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      const float v = x[i] + fb_load_coherent<TY>(yr + i);
+      const float v = fmaf(y_scale, fb_load_coherent<TY>(yr + i), x[i]);
       x[i] = v;
       row[i] = v;
     }
@@ -107,7 +107,7 @@ __global__ void ln_add_ln_kernel(const TY* y, const float* __restrict__ w1,
   const float r = 1.0f / sqrtf(fb_block_sum(q, scratch) * inv_w + eps);
   TO* o = out + base;
   for (int i = threadIdx.x; i < W; i += blockDim.x)
-    o[i] = fb_from_float<TO>((row[i] - mean) * r * w2[i] + b2[i]);
+    o[i] = fb_from_float<TO>((row[i] - mean) * r * w2[i] + (b2 != nullptr ? b2[i] : 0.f));
 }
 
 // The same for rows of whole groups of four elements on 16-byte boundaries: every
@@ -141,7 +141,7 @@ __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
 
 template <typename TY, typename TO>
 __global__ void ln_add_ln_vec_kernel(const TY* y, const float* __restrict__ w1,
-                                     const float* __restrict__ b1, float* resid,
+                                     const float* __restrict__ b1, float y_scale, float* resid,
                                      const float* __restrict__ w2, const float* __restrict__ b2,
                                      TO* __restrict__ out, int W, float eps, float inv_w,
                                      DepthMix mix) {
@@ -156,7 +156,8 @@ __global__ void ln_add_ln_vec_kernel(const TY* y, const float* __restrict__ w1,
   if (y != nullptr && w1 == nullptr) {
     for (int i = threadIdx.x; i < n4; i += blockDim.x) {
       const float4 a = ld4<float>(x + 4 * i), d = ld4<TY>(y + base + 4 * i);
-      const float4 v = make_float4(a.x + d.x, a.y + d.y, a.z + d.z, a.w + d.w);
+      const float4 v = make_float4(fmaf(y_scale, d.x, a.x), fmaf(y_scale, d.y, a.y),
+                                   fmaf(y_scale, d.z, a.z), fmaf(y_scale, d.w, a.w));
       st4<float>(x + 4 * i, v);
       row4[i] = v;
     }
@@ -202,7 +203,8 @@ __global__ void ln_add_ln_vec_kernel(const TY* y, const float* __restrict__ w1,
   }
   const float r = 1.0f / sqrtf(fb_block_sum(q, scratch) * inv_w + eps);
   for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-    const float4 v = row4[i], g = ld4<float>(w2 + 4 * i), h = ld4<float>(b2 + 4 * i);
+    const float4 v = row4[i], g = ld4<float>(w2 + 4 * i);
+    const float4 h = b2 != nullptr ? ld4<float>(b2 + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
     st4<TO>(out + base + 4 * i, make_float4((v.x - mean) * r * g.x + h.x, (v.y - mean) * r * g.y + h.y,
                                             (v.z - mean) * r * g.z + h.z, (v.w - mean) * r * g.w + h.w));
   }
@@ -257,15 +259,16 @@ __global__ void add_row_vector_kernel(float* x, const float* __restrict__ v, int
 }
 }  // namespace
 
-FB_API int fb_ln_add_ln(const void* y, int y_dtype, const float* w1, const float* b1, float* resid,
-                        const float* w2, const float* b2, void* out, int out_dtype, int T, int W,
-                        float eps, const float* mix_first, float* mix_kept,
+FB_API int fb_ln_add_ln(const void* y, int y_dtype, const float* w1, const float* b1, float y_scale,
+                        float* resid, const float* w2, const float* b2, void* out, int out_dtype,
+                        int T, int W, float eps, const float* mix_first, float* mix_kept,
                         const float* mix_weights, int mix_n, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && W > 0 && eps > 0.f, "ln_add_ln: bad sizes T=%d W=%d", T, W);
   FB_REQUIRE(resid != nullptr, "ln_add_ln: no residual rows");
   FB_REQUIRE(y == nullptr || ((w1 != nullptr) == (b1 != nullptr)),
              "ln_add_ln: the norm of y has a weight or a bias but not both");
-  FB_REQUIRE(out == nullptr || (w2 && b2), "ln_add_ln: the norm of the sum has no weight or bias");
+  FB_REQUIRE(out == nullptr || w2, "ln_add_ln: the norm of the sum has no weight");
+  FB_REQUIRE(y_scale == 1.0f || w1 == nullptr, "ln_add_ln: a constant on y goes with a plain sum");
   FB_REQUIRE((size_t)W * 4 <= 200 * 1024, "ln_add_ln: rows of %d do not fit shared memory", W);
   FB_REQUIRE(mix_n >= 0 && (mix_n == 0 || (mix_first && mix_kept && mix_weights)),
              "ln_add_ln: a depth-wise average of %d kept streams lacks an input", mix_n);
@@ -290,10 +293,11 @@ FB_API int fb_ln_add_ln(const void* y, int y_dtype, const float* w1, const float
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
     if (vec)                                                                                   \
       fb_launch(ln_add_ln_vec_kernel<TY, TO>, dim3(T), dim3(threads), smem, stream,            \
-                (const TY*)y, w1, b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W, mix);  \
+                (const TY*)y, w1, b1, y_scale, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W,  \
+                mix);                                                                          \
     else                                                                                       \
       fb_launch(ln_add_ln_kernel<TY, TO>, dim3(T), dim3(threads), smem, stream, (const TY*)y,  \
-                w1, b1, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W, mix);                \
+                w1, b1, y_scale, resid, w2, b2, (TO*)out, W, eps, 1.0f / (float)W, mix);       \
   } while (0)
   const int yd = y ? y_dtype : FB_F32, od = out ? out_dtype : FB_F32;
   FB_DISPATCH_DTYPE(yd, TY, FB_DISPATCH_DTYPE(od, TO, FB_LN_LAUNCH(TY, TO)));

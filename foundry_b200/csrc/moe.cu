@@ -24,12 +24,17 @@ namespace {
 
 __global__ void moe_route_kernel(const float* z, long long ld, const float* __restrict__ bias,
                                  int E, int top, int* __restrict__ chosen,
-                                 float* __restrict__ weights, int score, int groups, int keep) {
+                                 float* __restrict__ weights, int score, int groups, int keep,
+                                 const float* __restrict__ correction, int normalise,
+                                 float sum_floor, float weight_scale) {
   fb_pdl_launch();
   fb_pdl_wait();
-  // one warp per token; each lane keeps the experts lane, lane + 32, ... (up to 8 of them)
+  // one warp per token; each lane keeps the experts lane, lane + 32, ... (up to 8 of them).
+  // v[] is what the choice goes by (the score, plus `correction` where given); the
+  // weights come from the scores themselves (s_plain).
   __shared__ float s_all[256];
   __shared__ float s_group[256];
+  __shared__ float s_plain[256];
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31;
   float v[8];
@@ -39,9 +44,12 @@ __global__ void moe_route_kernel(const float* z, long long ld, const float* __re
     v[i] = -INFINITY;
     if (e < E) {
       const float x = __ldcg(z + (size_t)t * ld + e) + (bias != nullptr ? bias[e] : 0.f);
-      v[i] = score == 1 ? 1.0f / (1.0f + expf(-x)) : x;
+      const float sc = score == 1 ? 1.0f / (1.0f + expf(-x)) : x;
+      s_plain[e] = sc;
+      v[i] = correction != nullptr ? sc + correction[e] : sc;
     }
   }
+  __syncwarp();
   if (score == 1 && groups > 1) {
     // a group's score: the sum of its two largest (a group of one: that one); the `keep`
     // best groups stay, the lower index among equals
@@ -95,16 +103,21 @@ __global__ void moe_route_kernel(const float* z, long long ld, const float* __re
       if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
     }
     if (c == 0) first = best;  // values are chosen in falling order: the first is the largest
-    const float e = score == 1 ? best : expf(best - first);
+    if (at >= E) at = 0;  // only when every value left is NaN: any expert, never a wild index
+    const float e = score == 1 ? s_plain[at] : expf(best - first);
     sum += e;
     if (lane == c) mine = e;
-    if (at >= E) at = 0;  // only when every value left is NaN: any expert, never a wild index
     if (lane == 0) chosen[(size_t)t * top + c] = at;
 #pragma unroll
     for (int i = 0; i < 8; ++i)
       if (at == lane + 32 * i) v[i] = -INFINITY;
   }
-  if (lane < top) weights[(size_t)t * top + lane] = score == 1 ? mine : mine / sum;
+  // sigmoid scores: the chosen scores themselves, or (normalise) their shares of their sum
+  // plus `sum_floor`; both times `weight_scale`. Softmax over the chosen: mine / sum.
+  if (lane < top)
+    weights[(size_t)t * top + lane] =
+        score == 1 ? (normalise ? mine / (sum + sum_floor) * weight_scale : mine * weight_scale)
+                   : mine / sum;
 }
 
 template <typename T>
@@ -183,7 +196,8 @@ moe_experts_rows_kernel(const T* h, const T* __restrict__ gate_up, const T* __re
 
 FB_API int fb_moe_route(const float* z, long long ld, const float* bias, int E, int top,
                         int* chosen, float* weights, int T, int score, int groups, int keep,
-                        cudaStream_t stream) {
+                        const float* correction, int normalise, float sum_floor,
+                        float weight_scale, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && E > 0 && E <= 256 && top > 0 && top <= E && top <= 32 && ld >= E,
              "moe_route: %d experts (at most 256), %d chosen (at most 32)", E, top);
   FB_REQUIRE(score == 0 || score == 1, "moe_route: unknown scoring rule %d", score);
@@ -191,10 +205,13 @@ FB_API int fb_moe_route(const float* z, long long ld, const float* bias, int E, 
              (long long)keep * (E / groups) >= top,
              "moe_route: %d groups of %d experts, %d kept, %d chosen", groups, E, keep, top);
   FB_REQUIRE(score == 1 || groups == 1, "moe_route: groups need the sigmoid scores");
+  FB_REQUIRE(score == 1 || (correction == nullptr && !normalise && weight_scale == 1.0f),
+             "moe_route: a correction of the choice, shares of the sum and a constant on the "
+             "weights need the sigmoid scores");
   if (T == 0) return 0;
   // a warp per token
   fb_launch(moe_route_kernel, dim3(T), dim3(32), 0, stream, z, ld, bias, E, top, chosen, weights,
-            score, groups, keep);
+            score, groups, keep, correction, normalise, sum_floor, weight_scale);
   return fb_check_launch("moe_route");
 }
 

@@ -485,7 +485,32 @@ __global__ void unary_cast_kernel(const float* in, long long ld, T* __restrict__
     out[t * n + i] = fb_from_float<T>(act == 1 ? tanhf(v) : act == 2 ? r * r : v);
   }
 }
+
+// x[t, i] <- x[t, i] * sigmoid(gate[t, i]), in place: x in the activation type, the gate's
+// rows float32; the product is made in 32-bit and rounded once.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* x, long long ldx, const float* gate, long long ldg, int n) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
+    const float g = __ldcg(gate + t * ldg + i);
+    const float v = fb_to_float<T>(x[t * ldx + i]);
+    x[t * ldx + i] = fb_from_float<T>(v / (1.0f + expf(-g)));
+  }
+}
 }  // namespace
+
+FB_API int fb_sigmoid_gate(void* x, int dtype, long long ldx, const float* gate, long long ldg,
+                           int T, int n, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && n > 0 && ldx >= n && ldg >= n, "sigmoid_gate: bad sizes");
+  if (T == 0) return 0;
+  const int want = (n + 511) / 512;
+  const int parts = T >= 1024 ? (want < 4 ? want : 4) : (want < 64 ? want : 64);
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(sigmoid_gate_kernel<E>, dim3(T, parts), dim3(256), 0, stream,
+      (E*)x, ldx, gate, ldg, n)));
+  return fb_check_launch("sigmoid_gate");
+}
 
 FB_API int fb_token_shift_mix(const void* h, int dtype, float* state, long long state_stride,
                               long long prev_offset, const float* mu, void* out,

@@ -47,13 +47,16 @@ __device__ __forceinline__ void sg_load8<__nv_bfloat16>(const __nv_bfloat16* p, 
 
 // One block a token. Rows of `qkv` are [q: H x dim | k: G x dim | v: G x vdim] in
 // float32. Queries go to `q_out` in the activation type, keys and values into the
-// token's cache row.
+// token's cache row. `qk_norm` 0 leaves queries and keys as they are; `interleaved`
+// 1 turns elements (2i, 2i + 1) instead of (i, i + rot / 2); G may be 0 (a mixer that
+// reads another's keys and values has queries only).
 template <typename T>
 __global__ void head_norm_rope_cache_kernel(const float* qkv, long long ld, T* __restrict__ q_out,
                                             const float* __restrict__ wq,
                                             const float* __restrict__ wk, float eps,
-                                            int value_norm, const double* __restrict__ freq,
-                                            int rot, const int* __restrict__ positions,
+                                            int qk_norm, int value_norm,
+                                            const double* __restrict__ freq, int rot,
+                                            int interleaved, const int* __restrict__ positions,
                                             const int* __restrict__ seq_of_token,
                                             const int* __restrict__ page_table, int max_pages,
                                             T* __restrict__ k_cache, T* __restrict__ v_cache,
@@ -99,7 +102,7 @@ __global__ void head_norm_rope_cache_kernel(const float* qkv, long long ld, T* _
       ss = fmaf(x, x, ss);
     }
     ss = fb_warp_sum(ss);
-    const bool normed = is_q || is_k || value_norm;
+    const bool normed = (is_q || is_k) ? qk_norm != 0 : value_norm != 0;
     const float r = normed ? 1.0f / sqrtf(ss / (float)n + eps) : 1.0f;
     const float* w = is_q ? wq : is_k ? wk : nullptr;
     __syncwarp();
@@ -107,10 +110,11 @@ __global__ void head_norm_rope_cache_kernel(const float* qkv, long long ld, T* _
     __syncwarp();
     if (is_q || is_k) {
       for (int i = lane; i < half; i += 32) {
-        const float a = buf[i], b = buf[i + half];
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+        const float a = buf[ia], b = buf[ib];
         const float c = cs[i], s = cs[half + i];
-        buf[i] = a * c - b * s;
-        buf[i + half] = b * c + a * s;
+        buf[ia] = a * c - b * s;
+        buf[ib] = b * c + a * s;
       }
       __syncwarp();
     }
@@ -430,13 +434,15 @@ __global__ void attention_sigmoid_runs_kernel(const float* partial, int runs, T*
 
 FB_API int fb_head_norm_rope_cache_write(const float* qkv, long long ld, void* q_out, int dtype,
                                          const float* wq, const float* wk, float eps,
-                                         int value_norm, const double* freq, int rot,
-                                         const int* positions, const int* seq_of_token,
+                                         int qk_norm, int value_norm, const double* freq,
+                                         int rot, int interleaved, const int* positions,
+                                         const int* seq_of_token,
                                          const int* page_table, int max_pages, void* k_cache,
                                          void* v_cache, long long k_page, long long k_head,
                                          long long v_page, long long v_head, int T, int H, int G,
                                          int dim, int vdim, int write_cache, cudaStream_t stream) {
-  FB_REQUIRE(T >= 0 && H > 0 && G > 0 && dim > 0 && vdim > 0, "head_norm_rope_cache_write: bad sizes");
+  FB_REQUIRE(T >= 0 && H > 0 && G >= 0 && dim > 0 && vdim > 0, "head_norm_rope_cache_write: bad sizes");
+  FB_REQUIRE(G > 0 || !write_cache, "head_norm_rope_cache_write: no keys to write");
   FB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dim && (rot == 0 || freq != nullptr),
              "head_norm_rope_cache_write: %d rotated elements of %d", rot, dim);
   FB_REQUIRE(ld >= (long long)(H + G) * dim + (long long)G * vdim,
@@ -449,7 +455,8 @@ FB_API int fb_head_norm_rope_cache_write(const float* qkv, long long ld, void* q
   FB_REQUIRE(smem <= 48 * 1024, "head_norm_rope_cache_write: heads of %d do not fit", head_floats);
   const int parts = T <= 256 ? (heads + warps - 1) / warps : 1;  // few tokens: more blocks
   FB_DISPATCH_DTYPE(dtype, E, (fb_launch(head_norm_rope_cache_kernel<E>, dim3(T, parts), dim3(warps * 32),
-      smem, stream, qkv, ld, (E*)q_out, wq, wk, eps, value_norm, freq, rot, positions,
+      smem, stream, qkv, ld, (E*)q_out, wq, wk, eps, qk_norm, value_norm, freq, rot, interleaved,
+      positions,
       seq_of_token, page_table, max_pages, (E*)k_cache, (E*)v_cache, k_page, k_head, v_page,
       v_head, H, G, dim, vdim, write_cache, head_floats)));
   return fb_check_launch("head_norm_rope_cache_write");

@@ -839,8 +839,8 @@ FB_API int fb_latent_rows(const float* in, long long ld, void* a_out, int dtype,
                           const int* positions, const int* seq_of_token, const int* page_table,
                           int max_pages, void* cache, long long c_page, void* b_out, int T, int na,
                           int nb, int nrot, int write_cache, cudaStream_t stream) {
-  FB_REQUIRE(T >= 0 && na > 0 && nb > 0 && nrot >= 0 && rot_dims >= 0 && rot_dims <= nrot &&
-             rot_dims % 2 == 0, "latent_rows: bad sizes");
+  FB_REQUIRE(T >= 0 && na >= 0 && nb > 0 && nrot >= 0 && rot_dims >= 0 && rot_dims <= nrot &&
+             rot_dims % 2 == 0, "latent_rows: bad sizes");  // na = 0: no second latent
   FB_REQUIRE(ld >= (long long)na + nb + nrot, "latent_rows: rows of %lld are too short", ld);
   FB_REQUIRE(!write_cache || (cache && page_table && max_pages > 0), "latent_rows: no cache to write");
   if (T == 0) return 0;

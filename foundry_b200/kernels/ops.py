@@ -86,13 +86,14 @@ _SIGNATURES = {
     "fb_row_scales": [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_void_p, c_void_p, c_void_p],
-    "fb_ln_add_ln": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                     c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "fb_ln_add_ln": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                     c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int,
+                     c_void_p],
     "fb_softcap": [c_void_p, c_ll, c_float, c_void_p],
     "fb_head_norm_rope_cache_write": [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_float,
-                                      c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                      c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int, c_int,
-                                      c_int, c_int, c_int, c_int, c_void_p],
+                                      c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_attention_sigmoid": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
                              c_int, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_void_p, c_void_p,
                              c_ll, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -138,7 +139,8 @@ _SIGNATURES = {
                           c_float, c_void_p, c_float, c_float, c_float, c_void_p],
     "fb_attention_prefill_masked": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
                                     c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int,
-                                    c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p],
+                                    c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p,
+                                    c_void_p],
     "fb_token_shift_mix": [c_void_p, c_int, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "fb_state_tail_update": [c_void_p, c_int, c_ll, c_void_p, c_ll, c_ll, c_int, c_int, c_void_p,
@@ -154,8 +156,10 @@ _SIGNATURES = {
     "fb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_float, c_void_p,
                           c_ll, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_unary_cast": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "fb_add_into": [c_void_p, c_void_p, c_ll, c_void_p],
+    "fb_sigmoid_gate": [c_void_p, c_int, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p],
     "fb_moe_route": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-                     c_int, c_void_p],
+                     c_int, c_void_p, c_int, c_float, c_float, c_void_p],
     "fb_moe_experts_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p,
                             c_void_p],
@@ -1195,6 +1199,15 @@ def sum_planes(planes: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def add_into(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a += b, both float32 and contiguous, of one shape."""
+    if a.shape != b.shape:
+        raise KernelError(f"add_into: {tuple(a.shape)} += {tuple(b.shape)}")
+    _call("fb_add_into", _dev(a, "a", torch.float32), _dev(b, "b", torch.float32), a.numel(),
+          _stream())
+    return a
+
+
 def _tc_usable(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     K = x.shape[1]
     return (K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
@@ -1629,8 +1642,10 @@ class NormedDelta:
     that follows in the stream makes this sum in its own pass over the row
     (`ln_add_ln`); `settle` makes it alone."""
 
-    def __init__(self, values: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float):
+    def __init__(self, values: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                 scale: float = 1.0):
         self.values, self.weight, self.bias, self.eps = values, weight, bias, float(eps)
+        self.scale = float(scale)  # of a plain sum (no weight): resid += scale * values
 
     def settle(self, resid: torch.Tensor) -> None:
         ln_add_ln(resid, self, None, None, self.eps, None)
@@ -1665,8 +1680,11 @@ def ln_add_ln(resid: torch.Tensor, pending: Optional[NormedDelta], weight: Optio
     out = LN(resid; weight, bias) where `out` is given; float32 statistics."""
     T, W = resid.shape
     y = w1 = b1 = 0
-    y_code = F32
+    y_code, y_scale = F32, 1.0
     if pending is not None:
+        y_scale = float(getattr(pending, "scale", 1.0))
+        if y_scale != 1.0 and pending.weight is not None:
+            raise KernelError("ln_add_ln: a constant on the rows goes with a plain sum")
         if tuple(pending.values.shape) != (T, W) or pending.eps != float(eps):
             raise KernelError(f"ln_add_ln: pending rows {tuple(pending.values.shape)} eps "
                               f"{pending.eps} for resid {(T, W)} eps {eps}")
@@ -1677,10 +1695,12 @@ def ln_add_ln(resid: torch.Tensor, pending: Optional[NormedDelta], weight: Optio
     o = w2 = b2 = 0
     o_code = F32
     if out is not None:
-        if tuple(out.shape) != (T, W) or tuple(weight.shape) != (W,) or tuple(bias.shape) != (W,):
+        if tuple(out.shape) != (T, W) or tuple(weight.shape) != (W,) or (
+                bias is not None and tuple(bias.shape) != (W,)):
             raise KernelError(f"ln_add_ln: out {tuple(out.shape)}, weight {tuple(weight.shape)}")
         o, o_code = _dev(out, "out"), code_of(out.dtype)
-        w2, b2 = _dev(weight, "weight", torch.float32), _dev(bias, "bias", torch.float32)
+        w2 = _dev(weight, "weight", torch.float32)
+        b2 = 0 if bias is None else _dev(bias, "bias", torch.float32)  # a norm without bias
     m_first = m_kept = m_weights = m_n = 0
     if mix is not None:
         n = int(mix.n)
@@ -1691,7 +1711,7 @@ def ln_add_ln(resid: torch.Tensor, pending: Optional[NormedDelta], weight: Optio
         m_first = _dev(mix.first, "first", torch.float32)
         m_kept = _dev(mix.kept, "kept", torch.float32)
         m_weights, m_n = _dev(mix.weights, "weights", torch.float32), n
-    _call("fb_ln_add_ln", y, y_code, w1, b1, _dev(resid, "resid", torch.float32), w2, b2, o, o_code,
+    _call("fb_ln_add_ln", y, y_code, w1, b1, y_scale, _dev(resid, "resid", torch.float32), w2, b2, o, o_code,
           T, W, float(eps), m_first, m_kept, m_weights, m_n, _stream())
     return out
 
@@ -1802,7 +1822,9 @@ def attention_sink(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache,
         _check_kv_pair(k_cache, v_cache, G, k_row, vdim, q.dtype)
     if maps not in (1, 2) or (maps == 2) != (combine is not None):
         raise KernelError("attention_sink: two maps a head need `combine`, one map takes none")
-    plain_rule = softcap == 0.0 and sink_logits is None and maps == 1 and not values_in_keys
+    plain_rule = softcap == 0.0 and maps == 1 and not values_in_keys
+    if sink_logits is not None and tuple(sink_logits.shape) != (H,):
+        raise KernelError(f"attention_sink: {tuple(sink_logits.shape)} sink scores for {H} heads")
     if (SINK_ATTENTION_TC and plain_rule and not ctx.is_decode and q.dtype == torch.bfloat16
             and dim == vdim
             and dim in FAST_HEAD_DIMS and H // G <= 16 and k_cache.stride() == v_cache.stride()
@@ -1817,7 +1839,9 @@ def attention_sink(ctx, q: torch.Tensor, out: torch.Tensor, page_table, k_cache,
               _dev(page_table, "page_table", torch.int32), page_table.shape[1],
               k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
               ctx.n_seqs, q_blocks, H, G, dim, float(scale), window, keep_first,
-              1 if sink else 0, float(steep), _stream())
+              1 if sink else 0, float(steep),
+              0 if sink_logits is None else _dev(sink_logits, "sink_logits", torch.float32),
+              _stream())
         return out
     if (maps == 2 and not values_in_keys and not window and not sink and steep == 0.0
             and attention_maps_fits(ctx, q, dim, vdim, maps) and H // G <= 64
@@ -2035,12 +2059,14 @@ def head_norm_rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor,
                                wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
                                value_norm: bool, freq: Optional[torch.Tensor], positions,
                                seq_of_token, page_table, k_cache, v_cache, H: int, G: int,
-                               dim: int, vdim: int, write_cache: bool = True) -> torch.Tensor:
+                               dim: int, vdim: int, write_cache: bool = True,
+                               qk_norm: bool = True, pairing: str = "half") -> torch.Tensor:
     """Per-head RMS norms of queries and keys (weights [dim] shared by the heads, or
-    none), the rotation of their first 2 * len(freq) elements (element i with element
-    i + len(freq); `freq` float64), the values' RMS norm without weight where
-    `value_norm`; queries to `q_out`, keys and values into the token's cache row.
-    `qkv`: float32 rows [q | k | v]."""
+    none; `qk_norm` False: queries and keys stay as they are), the rotation of their first
+    2 * len(freq) elements (`pairing` "half": element i with element i + len(freq);
+    "interleaved": 2i with 2i + 1; `freq` float64), the values' RMS norm without weight
+    where `value_norm`; queries to `q_out`, keys and values into the token's cache row.
+    `qkv`: float32 rows [q | k | v]; with G = 0 rows of queries only (nothing is cached)."""
     T = qkv.shape[0]
     kp = vp = 0
     ks = vs = (0, 0)
@@ -2055,9 +2081,9 @@ def head_norm_rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor,
     _call("fb_head_norm_rope_cache_write", _dev(qkv, "qkv", torch.float32, contiguous=False),
           _rows(qkv, "qkv"), _dev(q_out, "q_out"), code_of(q_out.dtype),
           0 if wq is None else _dev(wq, "wq", torch.float32),
-          0 if wk is None else _dev(wk, "wk", torch.float32), float(eps), 1 if value_norm else 0,
-          0 if freq is None else _dev(freq, "freq", torch.float64), rot,
-          _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+          0 if wk is None else _dev(wk, "wk", torch.float32), float(eps), 1 if qk_norm else 0,
+          1 if value_norm else 0, 0 if freq is None else _dev(freq, "freq", torch.float64), rot,
+          _pairing_code(pairing), _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1], kp, vp, *ks, *vs,
           T, H, G, dim, vdim, 1 if write_cache else 0, _stream())
     return q_out
@@ -2267,6 +2293,17 @@ def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, per_head_weight: bool,
     return out
 
 
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """x <- x * sigmoid(gate) in place: x [T, n] in the activation type, gate float32 rows
+    [T, n] (a view with contiguous rows); the product in 32-bit, rounded once."""
+    T, n = x.shape
+    if tuple(gate.shape) != (T, n):
+        raise KernelError(f"sigmoid_gate: a gate of {tuple(gate.shape)} for rows {(T, n)}")
+    _call("fb_sigmoid_gate", _dev(x, "x", contiguous=False), code_of(x.dtype), _rows(x, "x"),
+          _dev(gate, "gate", torch.float32, contiguous=False), _rows(gate, "gate"), T, n, _stream())
+    return x
+
+
 def unary_cast(x: torch.Tensor, out: torch.Tensor, act: str = "identity") -> torch.Tensor:
     """out = act(x) rounded to out's dtype; x float32 rows (possibly strided)."""
     T, n = out.shape
@@ -2281,17 +2318,25 @@ MOE_SCORES = {"softmax_chosen": 0, "sigmoid": 1}
 
 def moe_route(z: torch.Tensor, bias: Optional[torch.Tensor], top: int, chosen: torch.Tensor,
               weights: torch.Tensor, score: str = "softmax_chosen", groups: int = 1,
-              keep: int = 1) -> None:
+              keep: int = 1, correction: Optional[torch.Tensor] = None,
+              normalise: bool = False, sum_floor: float = 0.0,
+              weight_scale: float = 1.0) -> None:
     """The `top` experts of every token and their weights from the router's float32
     rows `z` (+ `bias`). "softmax_chosen": the largest z, weighted by the softmax over
-    the chosen ones. "sigmoid": scores sigmoid(z); of `groups` equal groups of
-    neighbouring experts only the `keep` with the largest sum of their two best scores
-    can be chosen; the weights are the chosen scores themselves."""
+    the chosen ones. "sigmoid": scores s = sigmoid(z); the choice goes by s (+ `correction`,
+    float32 [E], which never enters a weight); of `groups` equal groups of neighbouring
+    experts only the `keep` with the largest sum of their two best choice values can be
+    chosen (the others count as minus infinity); the weights are the chosen s themselves or,
+    with `normalise`, s / (their sum + `sum_floor`), times `weight_scale`."""
     T, E = z.shape
+    if correction is not None and tuple(correction.shape) != (E,):
+        raise KernelError(f"moe_route: a correction of {tuple(correction.shape)} for {E} experts")
     _call("fb_moe_route", _dev(z, "z", torch.float32, contiguous=False), _rows(z, "z"),
           0 if bias is None else _dev(bias, "bias", torch.float32), E, top,
           _dev(chosen, "chosen", torch.int32), _dev(weights, "weights", torch.float32), T,
-          MOE_SCORES[score], int(groups), int(keep), _stream())
+          MOE_SCORES[score], int(groups), int(keep),
+          0 if correction is None else _dev(correction, "correction", torch.float32),
+          1 if normalise else 0, float(sum_floor), float(weight_scale), _stream())
 
 
 def moe_experts_rows(h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,

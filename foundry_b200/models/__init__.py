@@ -1,2 +1,2 @@
 """Built-in architectures; importing this package registers them."""
-from . import llama, rupotar, vikarax, vonulorn  # noqa: F401
+from . import kutepel, llama, rupotar, vikarax, vonulorn  # noqa: F401

@@ -4,7 +4,7 @@ from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Par
                    register_position_encoding)
 from . import (attention, block, differential_attention, embedding, junction,  # noqa: F401
                latent_attention, linear, mlp, moe, norm, parallel, recurrent, rope,
-               sigmoid_attention, sink_attention)  # (registration)
+               rotary_sink_attention, sigmoid_attention, sink_attention)  # (registration)
 from .embedding import EMBEDDINGS, register_embedding
 from .junction import JUNCTIONS, register_junction
 from .attention import GQAAttention

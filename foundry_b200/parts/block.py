@@ -284,3 +284,85 @@ class ScaledPreNormBlock(Part):
         normed = self.feed_forward_norm.add_norm(resid, mixed)
         ctx.reads_after_part, ctx.residual_sink = after_block, sink_after_block
         return self._leaves(self.feed_forward.forward(ctx, normed))
+
+
+@register_block("parallel_residual")
+class ParallelResidualBlock(Part):
+    """One norm whose output both parts read, their results joining the stream as one sum:
+
+        h = norm(x);  x <- x + m * (mixer(h) + feed_forward(h))
+
+    (without a feed-forward: x <- x + m * mixer(h)). The sum of the two results is
+    made in 32-bit where the second of them is finished: a feed-forward that says
+    `accepts_addend = True` takes the mixer's rows as `addend` and adds them where it
+    writes its own (the routed experts' combine does); otherwise a kernel adds them.
+    The block's output leaves as an `ops.ScaledDelta`, and the norm that runs next
+    makes `x += m * y` in its own pass over the row."""
+    replay_safe = True
+
+    def __init__(self, layer: LayerSpec, residual_scale: float = 1.0, *, dtype: torch.dtype,
+                 device: torch.device):
+        ctx = dict(dtype=dtype, device=device)
+        self.prefix = layer.prefix
+        self.names = dict(layer.names)
+        self.residual_scale = float(residual_scale)
+        self.mixer = MIXERS.build(layer.mixer, **ctx)
+        self.mixer_norm = NORMS.build(layer.mixer_norm, **ctx)
+        self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, **ctx)
+
+    def _named(self):
+        p, n = self.prefix, self.names
+        named = [(self.mixer_norm, f"{p}.{n['mixer_norm']}"), (self.mixer, f"{p}.{n['mixer']}")]
+        if self.feed_forward is not None:
+            named.append((self.feed_forward, f"{p}.{n['feed_forward']}"))
+        return named
+
+    def parts(self):
+        return [part for part, _ in self._named()]
+
+    def expected_tensors(self, prefix: str = "") -> Dict[str, ExpectedTensor]:
+        out: Dict[str, ExpectedTensor] = {}
+        for part, name in self._named():
+            out.update(part.expected_tensors(name))
+        return out
+
+    def load(self, prefix: str, fetch: Fetch) -> None:
+        for part, name in self._named():
+            part.load(name, fetch)
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def first_weight(self):
+        return first_weight_of(self.mixer)
+
+    def forward(self, ctx, resid: torch.Tensor, delta, cache):
+        from ..kernels import ops
+        after_block = getattr(ctx, "reads_after_part", None)
+        # the sum of two parts is not one product's epilogue: no norm is handed forward
+        ctx.residual_sink = None
+        normed = self.mixer_norm.add_norm(resid, delta)
+        if self.feed_forward is None:
+            ctx.reads_after_part = after_block
+            return ops.ScaledDelta(_as_float_rows(self.mixer.forward(ctx, normed, cache)),
+                                   self.residual_scale)
+        ctx.reads_after_part = first_weight_of(self.feed_forward)
+        mixed = _as_float_rows(self.mixer.forward(ctx, normed, cache))
+        ctx.reads_after_part = after_block
+        if getattr(self.feed_forward, "accepts_addend", False):
+            both = self.feed_forward.forward(ctx, normed, addend=mixed)
+        else:
+            both = ops.add_into(_as_float_rows(self.feed_forward.forward(ctx, normed)), mixed)
+        return ops.ScaledDelta(both, self.residual_scale)
+
+
+def _as_float_rows(y):
+    """A part's output as one float32 tensor (planes summed; 16-bit rows widened)."""
+    from ..kernels import ops
+    y = _as_rows(y)
+    if y.dtype != torch.float32:
+        wide = torch.empty(y.shape, dtype=torch.float32, device=y.device)
+        y = ops.cast(y, wide)
+    return y

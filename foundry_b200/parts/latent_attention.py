@@ -8,6 +8,11 @@
     p = exp(s) / (exp(sink_h) + sum exp(s))     a learned score per head joins the sum once
     out = Wo [heads' sum p v]
 
+Options: `q_rank = 0`, the queries come straight from the input, q = Wq h (tensor `q`;
+no `dq`, `dq.norm`, `uq`); `sink = False`, the ordinary softmax; `output_gate`, the heads'
+outputs side by side are multiplied, element by element, with sigmoid(Wg h) (tensor `g`;
+the gate reads the mixer's input) in front of Wo.
+
 The rotation turns neighbouring pairs (2i, 2i + 1) of the first `rot_dims`
 elements of the rotated part by position * base^(-2i / rot_dims).
 
@@ -49,8 +54,8 @@ class LatentAttention(Part):
 
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
                  q_rank: int, scale: float, eps: float, rot_base: float,
-                 rot_dims: Optional[int] = None, sink: bool = True, *, dtype: torch.dtype,
-                 device: torch.device):
+                 rot_dims: Optional[int] = None, sink: bool = True, output_gate: bool = False,
+                 *, dtype: torch.dtype, device: torch.device):
         rot_dims = rot_dim if rot_dims is None else int(rot_dims)
         if rot_dims % 2 or not 0 <= rot_dims <= rot_dim:
             raise ValueError(f"{rot_dims} rotated elements of a part of {rot_dim}")
@@ -58,7 +63,8 @@ class LatentAttention(Part):
             raise ValueError(f"latent rows of {kv_rank} + {rot_dim}: the attention kernel takes "
                              f"rows of at most 1024 with at most 768 latent elements")
         self.width, self.heads, self.dim, self.rot_dim, self.vdim = width, heads, dim, rot_dim, vdim
-        self.kv_rank, self.q_rank = kv_rank, q_rank
+        self.kv_rank, self.q_rank = kv_rank, int(q_rank or 0)
+        self.output_gate = bool(output_gate)
         self.scale, self.eps, self.sink = float(scale), float(eps), bool(sink)
         self.rot_dims, self.rot_base = rot_dims, float(rot_base)
         self.dtype, self.device = dtype, device
@@ -68,11 +74,16 @@ class LatentAttention(Part):
 
     def _shapes(self):
         W, H = self.width, self.heads
-        shapes = {"dq": (self.q_rank, W), "dq.norm": (self.q_rank,),
-                  "uq": (H * (self.dim + self.rot_dim), self.q_rank),
-                  "dkv": (self.row, W), "dkv.norm": (self.kv_rank,),
+        shapes = {"dkv": (self.row, W), "dkv.norm": (self.kv_rank,),
                   "uk": (H * self.dim, self.kv_rank), "uv": (H * self.vdim, self.kv_rank),
                   "o": (W, H * self.vdim)}
+        if self.q_rank:
+            shapes.update({"dq": (self.q_rank, W), "dq.norm": (self.q_rank,),
+                           "uq": (H * (self.dim + self.rot_dim), self.q_rank)})
+        else:
+            shapes["q"] = (H * (self.dim + self.rot_dim), W)
+        if self.output_gate:
+            shapes["g"] = (H * self.vdim, W)
         if self.sink:
             shapes["sink"] = (H,)
         return shapes
@@ -83,14 +94,19 @@ class LatentAttention(Part):
     def load(self, prefix: str, fetch: Fetch) -> None:
         f = lambda n: fetch(f"{prefix}.{n}")
         H, d, e, r = self.heads, self.dim, self.vdim, self.kv_rank
-        self.down = torch.cat([f("dq"), f("dkv")], 0).contiguous()  # one product for both latents
-        self.uq, self.o = f("uq").contiguous(), f("o").contiguous()
+        # one product for everything that reads the mixer's input: the query latent (or
+        # the queries themselves), the gate, the key-value latent with the rotated key part
+        first = [f("dq")] if self.q_rank else [f("q")]
+        self.down = torch.cat(first + [f("dkv")] + ([f("g")] if self.output_gate else []),
+                              0).contiguous()
+        self.uq = f("uq").contiguous() if self.q_rank else None
+        self.o = f("o").contiguous()
         # per head: [r, d] so that (plain query) x this^T is the query against the latent
         self.uk_t = f("uk").view(H, d, r).transpose(1, 2).contiguous()
         self.uv = f("uv").view(H, e, r).contiguous()
         # per head [k_plain rows | v rows]: one product expands a step's latent rows
         self.expand = torch.cat([f("uk").view(H, d, r), self.uv], 1).reshape(H * (d + e), r).contiguous()
-        self.q_norm = f("dq.norm").to(torch.float32).contiguous()
+        self.q_norm = f("dq.norm").to(torch.float32).contiguous() if self.q_rank else None
         self.kv_norm = f("dkv.norm").to(torch.float32).contiguous()
         self.sink_logits = f("sink").to(torch.float32).contiguous() if self.sink else None
 
@@ -109,15 +125,24 @@ class LatentAttention(Part):
         H, d, c, e, r = self.heads, self.dim, self.rot_dim, self.vdim, self.kv_rank
         act = dict(dtype=x.dtype, device=x.device)
         table = ctx.page_table(cache.group)
-        down = product_f32(x, self.down)  # [T, q_rank | kv_rank | rot_dim]
+        # [T, q_rank (or the queries, H (d + c)) | kv_rank | rot_dim | the gate, H e]
+        down = product_f32(x, self.down)
+        n_first = self.q_rank or H * (d + c)
+        gate = down[:, n_first + self.row:] if self.output_gate else None
         cq = torch.empty((T, self.q_rank), **act)
         expanded = (getattr(ctx, "fresh", False) and r % 8 == 0 and c % 8 == 0 and d % 8 == 0
                     and e % 8 == 0 and ops.attention_maps_fits(ctx, cq, d + c, e, 1))
         rows = torch.empty((T, self.row), **act) if expanded else None
-        ops.latent_rows(down, cq, self.q_norm, self.kv_norm, self.eps, self.freq, self.rot_dims,
-                        ctx.positions, ctx.seq_of_token, table, cache.k, r, c,
-                        write_cache=cache.writes, rows_out=rows)
-        q = product_f32(cq, self.uq)  # [T, H (d + c)]
+        if self.q_rank:
+            ops.latent_rows(down, cq, self.q_norm, self.kv_norm, self.eps, self.freq,
+                            self.rot_dims, ctx.positions, ctx.seq_of_token, table, cache.k, r, c,
+                            write_cache=cache.writes, rows_out=rows)
+            q = product_f32(cq, self.uq)  # [T, H (d + c)]
+        else:  # no query latent: the kernel norms and caches the key-value side only
+            ops.latent_rows(down[:, n_first:], cq, self.kv_norm, self.kv_norm, self.eps,
+                            self.freq, self.rot_dims, ctx.positions, ctx.seq_of_token, table,
+                            cache.k, r, c, write_cache=cache.writes, rows_out=rows)
+            q = down[:, :n_first]
         if expanded:
             q_full = torch.empty((T, H, d + c), **act)
             ops.split_rotate(q, None, q_full, d, self.freq, self.rot_dims, ctx.positions,
@@ -128,6 +153,8 @@ class LatentAttention(Part):
             ops.attention_maps_rows(ctx, q_full.view(T, H * (d + c)), out, kv[:, :, :d],
                                     rows[:, r:], kv[:, :, d:], H, d + c, e, self.scale,
                                     sink_logits=self.sink_logits)
+            if gate is not None:
+                ops.sigmoid_gate(out, gate)
             return product_to_residual(ctx, out, self.o)
         q_plain = torch.empty((T, H * d), **act)
         q_wide = torch.empty((T, H, self.row), **act)
@@ -145,4 +172,6 @@ class LatentAttention(Part):
                                values_in_keys=True)
         out = torch.empty((T, H, e), **act)
         ops.head_products(mixed.view(T, H, r), self.uv, out)
+        if gate is not None:
+            ops.sigmoid_gate(out.view(T, H * e), gate)
         return product_to_residual(ctx, out.view(T, H * e), self.o)

@@ -3,9 +3,12 @@
     z = W_router h (+ b)   (32-bit). Two scoring rules:
     "softmax_chosen": the `top` experts with the largest z are chosen (the lower index
         among equals) and weighted by the softmax over the chosen z only
-    "sigmoid": s = sigmoid(z); the experts form `groups` equal groups of neighbours, a
-        group's score is the sum of its two largest s, only experts of the `keep` best
-        groups can be chosen; the `top` largest s are chosen and weighted by s itself
+    "sigmoid": s = sigmoid(z); the choice goes by c = s (+ a learnt correction per expert,
+        `choice_correction`, which never enters a weight); the experts form `groups` equal
+        groups of neighbours, a group's score is the sum of its two largest c, only experts
+        of the `keep` best groups can be chosen; the `top` largest c are chosen and weighted
+        by s itself or (`normalise`) by s / (the chosen experts' sum of s + `sum_floor`),
+        times `weight_scale`
     expert:  g = min(W_gate h, limit);  u = clamp(W_up h, -limit, limit)
              y = W_down (g * sigmoid(alpha g) * (u + shift))
              (limit = infinity, alpha = 1, shift = 0:  W_down (silu(g) * u))
@@ -13,7 +16,8 @@
           SiLU form that every token uses, where `shared_ff` gives it a size)
 
 The experts' tensors are `<prefix>.e<i>.gate|up|down`, the router's
-`<prefix>.router` and (with `router_bias`) `<prefix>.router.b`, the shared
+`<prefix>.router`, (with `router_bias`) `<prefix>.router.b` and (with
+`choice_correction`) `<prefix>.<correction_name>`, the shared
 expert's `<prefix>.shared.gate|up|down`; the routed ones are stacked at load
 time so that a kernel reaches any expert by index. Every constant is a parameter.
 """
@@ -34,11 +38,15 @@ from .products import product_f32
 @register_feed_forward("routed_experts")
 class RoutedExperts(Part):
     replay_safe = True
+    accepts_addend = True  # forward(ctx, x, addend=rows): the rows join the experts' sum
 
     def __init__(self, width: int, ff: int, experts: int, top: int, limit: float = float("inf"),
                  alpha: float = 1.702, shift: float = 1.0, score: str = "softmax_chosen",
                  groups: int = 1, keep: int = 1, router_bias: bool = True, shared_ff: int = 0,
-                 shared_name: str = "shared", *, dtype: torch.dtype, device: torch.device):
+                 shared_name: str = "shared", choice_correction: bool = False,
+                 correction_name: str = "correction", normalise: bool = False,
+                 sum_floor: float = 0.0, weight_scale: float = 1.0, *, dtype: torch.dtype,
+                 device: torch.device):
         if not 1 <= top <= min(experts, 32) or experts > 256:
             raise ValueError(f"{top} of {experts} experts: the router takes up to 256 experts and "
                              f"chooses up to 32")
@@ -52,6 +60,13 @@ class RoutedExperts(Part):
         self.limit, self.alpha, self.shift = float(limit), float(alpha), float(shift)
         self.score, self.groups, self.keep = score, int(groups), int(keep)
         self.has_router_bias = bool(router_bias)
+        if (choice_correction or normalise or weight_scale != 1.0) and score != "sigmoid":
+            raise ValueError("a correction of the choice, shares of the chosen scores' sum and "
+                             "a constant on the weights need the sigmoid scores")
+        self.has_correction, self.correction_name = bool(choice_correction), correction_name
+        self.normalise, self.sum_floor = bool(normalise), float(sum_floor)
+        self.weight_scale = float(weight_scale)
+        self.correction = None
         self.dtype, self.device = dtype, device
         self.router_bias = None
         self.shared_name = shared_name
@@ -64,6 +79,8 @@ class RoutedExperts(Part):
         out = {f"{prefix}.router": ExpectedTensor((self.experts, self.width))}
         if self.has_router_bias:
             out[f"{prefix}.router.b"] = ExpectedTensor((self.experts,))
+        if self.has_correction:
+            out[f"{prefix}.{self.correction_name}"] = ExpectedTensor((self.experts,))
         if self.shared is not None:
             out.update(self.shared.expected_tensors(f"{prefix}.{self.shared_name}"))
         for e in range(self.experts):
@@ -76,6 +93,9 @@ class RoutedExperts(Part):
         self.router = fetch(f"{prefix}.router").contiguous()
         if self.has_router_bias:
             self.router_bias = fetch(f"{prefix}.router.b").to(torch.float32).contiguous()
+        if self.has_correction:
+            self.correction = fetch(f"{prefix}.{self.correction_name}").to(
+                torch.float32).contiguous()
         if self.shared is not None:
             self.shared.load(f"{prefix}.{self.shared_name}", fetch)
         # [E, 2 ff, W]: an expert's gate rows, then its up rows;  [E, W, ff]
@@ -88,17 +108,22 @@ class RoutedExperts(Part):
     def first_weight(self):
         return self.router
 
-    def forward(self, ctx, x):
+    def forward(self, ctx, x, addend=None):
+        """`addend` (float32 [T, width]): rows that join the sum where the chosen experts'
+        rows are combined (the result of a part that ran beside this one)."""
         T = x.shape[0]
         z = product_f32(x, self.router)
         chosen = torch.empty((T, self.top), dtype=torch.int32, device=x.device)
         weights = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
         ops.moe_route(z, self.router_bias, self.top, chosen, weights, self.score, self.groups,
-                      self.keep)
+                      self.keep, correction=self.correction, normalise=self.normalise,
+                      sum_floor=self.sum_floor, weight_scale=self.weight_scale)
         # the shared expert's rows join the sum where the chosen experts' rows are combined
-        shared = None
+        shared = addend
         if self.shared is not None:
             shared = product_f32(self.shared.hidden(ops.plain(x)), self.shared.down.weight)
+            if addend is not None:
+                ops.add_into(shared, addend)
         out = torch.empty((T, self.width), dtype=torch.float32, device=x.device)
         if not (ops.moe_grouped_fits(self.width) and ops.moe_grouped_fits(self.ff)):
             # sizes the grouped kernels do not take: every token streams its own experts

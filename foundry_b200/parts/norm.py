@@ -59,14 +59,15 @@ class RMSNorm(Part):
 class LayerNorm(Part):
     """(x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b with 32-bit statistics
     (csrc/layernorm.cu). The tensors are `<prefix><weight_suffix>` and
-    `<prefix><bias_suffix>`. Beside normalising a part's input (`add_norm`) it
+    `<prefix><bias_suffix>`; `bias_suffix = None` is the norm without a bias. Beside normalising a part's input (`add_norm`) it
     may stand behind a part: `pending(y)` says that LN(y) is still to join the
     residual, and the next `add_norm` (or `NormedDelta.settle`) makes that sum in
     the same pass."""
     replay_safe = True
 
     def __init__(self, size: int, eps: float, weight_suffix: str = ".weight",
-                 bias_suffix: str = ".bias", *, dtype: torch.dtype, device: torch.device):
+                 bias_suffix: Optional[str] = ".bias", *, dtype: torch.dtype,
+                 device: torch.device):
         self.size, self.eps = size, float(eps)
         self.weight_suffix, self.bias_suffix = weight_suffix, bias_suffix
         self.dtype, self.device = dtype, device
@@ -74,29 +75,38 @@ class LayerNorm(Part):
         self.bias: Optional[torch.Tensor] = None
 
     def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
-        return {f"{prefix}{self.weight_suffix}": ExpectedTensor((self.size,)),
-                f"{prefix}{self.bias_suffix}": ExpectedTensor((self.size,))}
+        out = {f"{prefix}{self.weight_suffix}": ExpectedTensor((self.size,))}
+        if self.bias_suffix is not None:
+            out[f"{prefix}{self.bias_suffix}"] = ExpectedTensor((self.size,))
+        return out
 
     def load(self, prefix: str, fetch: Fetch) -> None:
         self.weight = fetch(f"{prefix}{self.weight_suffix}").to(torch.float32).contiguous()
-        self.bias = fetch(f"{prefix}{self.bias_suffix}").to(torch.float32).contiguous()
+        if self.bias_suffix is not None:
+            self.bias = fetch(f"{prefix}{self.bias_suffix}").to(torch.float32).contiguous()
 
     def pending(self, values: torch.Tensor) -> ops.NormedDelta:
+        if self.bias is None:
+            raise ValueError("a layer norm without a bias cannot stand behind a part")
         return ops.NormedDelta(values, self.weight, self.bias, self.eps)
 
     def add_norm(self, resid: torch.Tensor, delta, out: Optional[torch.Tensor] = None):
-        """resid += delta (None, a tensor, split-K planes, an `ops.NormedDelta` whose norm
-        is applied on the way, or an `ops.DepthMix`, which also replaces the stream by
-        its weighted sum); returns LN(resid) in the activation dtype."""
+        """resid += delta (None, a tensor, split-K planes, an `ops.ScaledDelta` that joins
+        times its constant, an `ops.NormedDelta` whose norm is applied on the way, or an
+        `ops.DepthMix`, which also replaces the stream by its weighted sum); returns
+        LN(resid) in the activation dtype."""
         mix = None
         if isinstance(delta, ops.DepthMix):  # the stream is a weighted sum over kept streams
             mix, delta = delta, delta.pending
             if delta is not None and delta.eps != self.eps:
                 mix, delta = None, mix.settle(resid)
+        scale = 1.0
+        if isinstance(delta, ops.ScaledDelta):  # resid += scale * values
+            delta, scale = delta.values, delta.scale
         if isinstance(delta, ops.Planes):
             delta = delta.sum(torch.float32)
         if delta is not None and not isinstance(delta, ops.NormedDelta):
-            delta = ops.NormedDelta(delta, None, None, self.eps)  # a plain sum
+            delta = ops.NormedDelta(delta, None, None, self.eps, scale)  # a plain sum
         if delta is not None and delta.eps != self.eps:  # one pass takes one eps
             delta = delta.settle(resid)
         if out is None:

@@ -49,6 +49,26 @@ def llama3_inv_freq(head_dim: int, theta: float, factor: float, low_freq_factor:
     return np.where(medium, blended, scaled).astype(F)
 
 
+def banded_frequencies(dims: int, base: float, factor: float = 1.0, low: float = 1.0,
+                       high: float = 1.0, original: float = 0.0) -> np.ndarray:
+    """float64 frequencies f_i = base^(-2i / dims), i < dims / 2, for kernels that make the
+    angle as a 64-bit product with the position. With `original` > 0 they are scaled by
+    wavelength l = 2 pi / f in three bands: kept where l < original / high; f / factor
+    where l > original / low; between the two blended,
+    s = (original / l - low) / (high - low),  f' = (1 - s) f / factor + s f."""
+    if dims < 0 or dims % 2:
+        raise ValueError(f"rotary width {dims} is not an even number")
+    f = np.power(np.float64(base), -2.0 * np.arange(dims // 2, dtype=np.float64) / max(1, dims))
+    if not original:
+        return f
+    wavelength = 2.0 * math.pi / f
+    with np.errstate(divide="ignore", invalid="ignore"):
+        blend = (original / wavelength - low) / (high - low) if high != low else np.ones_like(f)
+    mixed = (1.0 - blend) * f / factor + blend * f
+    return np.where(wavelength < original / high, f,
+                    np.where(wavelength > original / low, f / factor, mixed))
+
+
 class _Rotary(Part):
     attention_factor = 1.0
     pairing = "half"  # src/models/llama/rotary_emb.rs:76-85 (rotate_half)
