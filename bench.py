@@ -501,7 +501,7 @@ def main() -> int:
                         help="launch decode kernels one by one (for profilers)")
     parser.add_argument("--beside", default="llama",
                         help="with --design: the designs to time beside it, with commas between them")
-    parser.add_argument("--design", default=None, choices=["rupotar", "vonulorn", "vikarax"],
+    parser.add_argument("--design", default=None, choices=["rupotar", "vonulorn", "vikarax", "kutepel"],
                         help="instead of the default workload: stacks of this design at real layer "
                              "sizes beside Llama stacks of equal size (prefill and decode "
                              "throughput, per-kernel device times)")

@@ -94,7 +94,42 @@ def _vikarax(layers, width, heads, kv_heads, dim, ff, vocab, chunk=1024, state=1
             "logit_softcap": 30.0, "layers": stack}
 
 
+def _kutepel(layers, width, heads, kv_heads, dim, ff, vocab, kv_rank, experts=16, top=2) -> Dict:
+    """A Kutepel stack of real layer sizes: grouped attention with a sink and latent
+    attention in turn, every third layer of the first kind reading the keys and values
+    of the one before it; every layer with routed experts a quarter as wide as the dense
+    feed-forward of the size (four groups of experts of which two are kept). The grouped
+    heads are rotated whole, in the frequency bands of an eightfold stretch of 8,192
+    positions; the latent attention rotates half a head's size beside it."""
+    stack = []
+    owners = []  # attention layers with keys and values of their own
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                     "scale": dim ** -0.5,
+                     "rot": {"base": 500000.0, "dims": dim,
+                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            if i % 6 == 4 and owners:
+                mixer["kv_from"] = owners[-1]
+            else:
+                owners.append(i)
+            kind = "attention"
+        else:
+            mixer = {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim,
+                     "kv_rank": kv_rank, "scale": (dim + dim // 2) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": dim // 2}}
+            kind = "latent_attention"
+        mlp = {"kind": "moe", "expert": {"ff": ff // 4},
+               "router": {"experts": experts, "top": top, "scale": 2.5,
+                          "groups": {"count": 4, "keep": 2}}}
+        stack.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Kutepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "residual_mult": 0.7, "layers": stack}
+
+
 PRESETS: Dict[str, Dict] = {
+    "kutepel-1b-layers": _kutepel(6, 2048, 32, 8, 64, 8192, 32000, 256),
+    "kutepel-3b-layers": _kutepel(6, 3072, 24, 8, 128, 8192, 32000, 512),
     "vikarax-1b-layers": _vikarax(6, 2048, 32, 8, 64, 8192, 32000),
     "vikarax-3b-layers": _vikarax(6, 3072, 24, 8, 128, 8192, 32000),
     "vonulorn-1b-layers": _vonulorn(6, 2048, 32, 8, 64, 8192, 32000, 256, 768),
