@@ -797,7 +797,11 @@ attn_decode_kernel(const AttnParams p) {
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) M = fmaxf(M, sM[w * 16 + row]);
-    float L = 0.f, acc = 0.f;
+    // a sink's term joins the sum once: in the range that holds the sequence's first page
+    const float sink_l2 = (p.sink_logits != nullptr && split == 0)
+                              ? p.sink_logits[kvh * G + row] * LOG2E : -INFINITY;
+    M = fmaxf(M, sink_l2);
+    float L = sink_l2 == -INFINITY ? 0.f : exp2f(sink_l2 - M), acc = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = sM[w * 16 + row];
@@ -962,7 +966,7 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
                                int Kh, int D, float scale, int splits, int stages, int cluster,
                                float* ws_o, float* ws_ml, int* counters,
                                const void* next, long long next_bytes, int trigger_next,
-                               cudaStream_t stream) {
+                               const float* sink_logits, cudaStream_t stream) {
   FB_REQUIRE(next_bytes >= 0 && next_bytes % 16 == 0 && ((uintptr_t)next % 16) == 0,
              "attention_decode: the prefetch range must be 16-byte aligned and a multiple of 16 bytes");
   int rc = check_common("attention_decode", n_seqs, A, Kh, D, q_stride, out_stride, q, k_cache,
@@ -988,6 +992,7 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
   p.ws_o = ws_o; p.ws_ml = ws_ml; p.counters = counters;
   p.next = next; p.next_bytes = next_bytes;
   p.trigger_next = trigger_next ? 1 : 0;
+  p.sink_logits = sink_logits;
   FB_REQUIRE(stages == 2 || stages == 3, "attention_decode: %d page buffers (2 or 3)", stages);
   if (stages == 2) {
     switch (D) {
@@ -1074,5 +1079,6 @@ FB_API int fb_attention_decode_static(const void* q, long long q_stride, void* o
   float* ws_ml = ws_o + units * 16 * D;
   return fb_attention_decode(q, q_stride, out, out_stride, cu_tokens, kv_lens, page_table,
                              max_pages, k_cache, v_cache, page_stride, head_stride, n_seqs, A, Kh,
-                             D, scale, splits, 3, 1, ws_o, ws_ml, counters, nullptr, 0, 0, stream);
+                             D, scale, splits, 3, 1, ws_o, ws_ml, counters, nullptr, 0, 0, nullptr,
+                             stream);
 }

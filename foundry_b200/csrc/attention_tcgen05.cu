@@ -63,6 +63,10 @@ struct FaParams {
   const int* page_table;
   int max_pages, n_seqs, A, Kh;
   float scale_log2;
+  // float32 per query head, or null: a sink's score. The softmax's sum has one more
+  // term exp(sink_logits[head]) that has no key and no value: it starts the running
+  // maximum and the sum.
+  const float* sink_logits;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -244,6 +248,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int qpos = pos0 + row;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
+    if (p.sink_logits != nullptr) { m_ref = p.sink_logits[head] * LOG2E; l = 1.f; }
     bool ok = true;
     fb_pdl_wait();
     for (int j = 0; j < n_pages && ok; ++j) {
@@ -431,7 +436,8 @@ FB_API int fb_attention_prefill_tc(const void* q, long long q_stride, int T, voi
                                    const int* page_table, int max_pages, const void* k_cache,
                                    const void* v_cache, long long page_stride,
                                    long long head_stride, int n_pages, int n_seqs, int q_blocks,
-                                   int A, int Kh, int D, float scale, cudaStream_t stream) {
+                                   int A, int Kh, int D, float scale, const float* sink_logits,
+                                   cudaStream_t stream) {
   FB_REQUIRE(D == 64 || D == 128, "attention_tc: head size %d is not built (64, 128)", D);
   FB_REQUIRE(n_seqs > 0 && A > 0 && Kh > 0 && A % Kh == 0 && T > 0 && n_pages > 0,
              "attention_tc: bad sizes");
@@ -463,6 +469,7 @@ FB_API int fb_attention_prefill_tc(const void* q, long long q_stride, int T, voi
   p.cu_tokens = cu_tokens; p.kv_lens = kv_lens; p.page_table = page_table;
   p.max_pages = max_pages; p.n_seqs = n_seqs; p.A = A; p.Kh = Kh;
   p.scale_log2 = scale * LOG2E;
+  p.sink_logits = sink_logits;
   return D == 64 ? launch<64>(mq, mk, mv, p, q_blocks, stream)
                  : launch<128>(mq, mk, mv, p, q_blocks, stream);
 }

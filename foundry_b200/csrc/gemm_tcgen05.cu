@@ -191,6 +191,156 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// --------------------------------------------------------------------- grouped
+// Many small products in one launch: the rows of A are sorted into groups (the
+// tokens of a routed feed-forward, sorted by expert), group e owns the rows
+// [starts[e], starts[e + 1]) and meets its own B (the weights of expert e: rows
+// [e * rows_b, (e + 1) * rows_b) of one stacked matrix):
+//   out[i, j] = sum_k A[i, k] * B[group(i) * rows_b + j, k]
+// One CTA computes one 128 x BN tile as above. `starts` lives on the device (the
+// kernel that sorted the rows wrote it), so nothing of the launch depends on the
+// counts: the grid holds `slots` row tiles, an upper bound of the sum over groups
+// of ceil(rows / 128), and a CTA finds its (group, row tile) by walking `starts`;
+// a CTA beyond the last tile returns at once. A group's last tile also reads the
+// next group's first rows (or zeros behind the last row); those rows of the
+// accumulator are not stored.
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a,
+                       const __grid_constant__ CUtensorMap map_b, const GemmParams p,
+                       const int* starts, int groups) {
+  constexpr int STAGES = Smem<BN>::STAGES;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * Smem<BN>::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_b = blockIdx.y;
+  const int nkb = (p.K + BK - 1) / BK;
+
+  // `starts` is the work of an earlier kernel: nothing is known before the wait
+  fb_pdl_wait();
+  int slot = blockIdx.x, group = 0, row0 = 0, row_end = 0;
+  for (; group < groups; ++group) {
+    const int first = __ldcg(starts + group), last = __ldcg(starts + group + 1);
+    const int n_tiles = (last - first + BM - 1) / BM;
+    if (slot < n_tiles) {
+      row0 = first + slot * BM;
+      row_end = last;
+      break;
+    }
+    slot -= n_tiles;
+  }
+  if (group >= groups) return;  // (every thread of the CTA alike: no tile for this slot)
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int b_row = group * p.rows_b + tile_b * BN;  // first row of this tile in the stacked B
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+        if (i >= STAGES && !mbar_wait(&empty[s], phase ^ 1u, abort_flag, 1, i)) break;
+        uint8_t* a_dst = tiles + s * Smem<BN>::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + Smem<BN>::A_BYTES;
+        mbar_expect_tx(&full[s], Smem<BN>::STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, &full[s], i * BK, row0);
+        tma_load_2d(b_dst, &map_b, &full[s], i * BK, b_row);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+        ok = mbar_wait(&full[s], phase, abort_flag, 2, i);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles + s * Smem<BN>::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + Smem<BN>::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          umma(tmem_base, make_desc(a_addr + k * UMMA_K * 2), make_desc(b_addr + k * UMMA_K * 2),
+               idesc, (i | k) != 0 ? 1u : 0u);
+        }
+        tc_commit(&empty[s]);
+      }
+      if (ok) tc_commit(acc_full);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    const long long i_global = (long long)row0 + quarter * 32 + lane;
+    const bool ok = mbar_wait(acc_full, 0, abort_flag, 3, 0);
+    tc_fence_after();
+    if (ok) {
+      GemmParams mine = p;      // rows of the next group are beyond this tile's bound
+      mine.rows_a = row_end;
+      float* out_f = (float*)p.out;
+      __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
+      constexpr int CHUNK = (BN % 32 == 0) ? 32 : 16;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += CHUNK) {
+        float v[CHUNK];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
+        if constexpr (CHUNK == 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+        } else {
+          uint32_t r[16];
+          tmem_ld16(taddr, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
+        }
+        store_chunk<CHUNK>(mine, v, i_global, (long long)tile_b * BN + c, lane, out_f, out_h);
+      }
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ persistent
 // The same product for many token rows, as one CTA per SM that walks over
 // tiles (tile index = blockIdx.x, += gridDim.x; the A tile index runs fastest,
@@ -404,6 +554,64 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
 }
 
 }  // namespace
+
+namespace {
+template <int BN>
+int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
+                   const int* starts, int groups, cudaStream_t stream) {
+  static bool configured[64] = {};
+  if (fb_first_use_on_device(configured)) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_grouped_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Smem<BN>::BYTES);
+    if (e != cudaSuccess) return fb_fail(2, "gemm_tc_grouped: shared memory opt-in: %s", cudaGetErrorString(e));
+  }
+  fb_launch(gemm_tc_grouped_kernel<BN>, grid, dim3(THREADS), Smem<BN>::BYTES, stream, ma, mb, p,
+            starts, groups);
+  return fb_check_launch("gemm_tc_grouped");
+}
+}  // namespace
+
+// The grouped product (see `gemm_tc_grouped_kernel`): a [rows_a, K] bf16 with rows
+// sorted by group, `starts` [groups + 1] int32 on the device (starts[groups] <=
+// rows_a), b [groups * rows_b, K] bf16 (the groups' matrices stacked);
+// out[i * ldo + j], float32 (out_f32) or bf16, j < rows_b. `slots`: at least the sum
+// over groups of ceil(rows of the group / 128); rows_a / 128 + groups always is.
+FB_API int fb_gemm_tc_grouped(const void* a, long long lda, int rows_a, const void* b,
+                              long long ldb, int rows_b, int K, const int* starts, int groups,
+                              int slots, void* out, long long ldo, int out_f32,
+                              cudaStream_t stream) {
+  FB_REQUIRE(rows_a > 0 && rows_b > 0 && K > 0 && groups > 0 && slots > 0 && starts != nullptr,
+             "gemm_tc_grouped: bad sizes %d x %d x %d in %d groups", rows_a, rows_b, K, groups);
+  FB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
+                 ((uintptr_t)b % 16) == 0,
+             "gemm_tc_grouped: K, the row strides and the operands must keep 16-byte alignment");
+  FB_REQUIRE(rows_b % 16 == 0 && ldo >= rows_b, "gemm_tc_grouped: %d features a group (a multiple "
+             "of 16) in rows of %lld", rows_b, ldo);
+  bind_status_mirror(stream);
+  // the widest tile that divides a group's features: a tile never spans two groups
+  int bn = 256;
+  while (rows_b % bn) bn >>= 1;
+  GemmParams p{};
+  p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
+  p.kblocks_per_split = (K + BK - 1) / BK;
+  p.stride_a = ldo; p.stride_b = 1; p.split_stride = 0;
+  p.out = out; p.out_f32 = out_f32; p.epilogue = 0; p.glu_act = 0; p.constant_operand = 2;
+  p.full_tiles = 0; p.tail_splits = 1; p.tail_kblocks = p.kblocks_per_split;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, rows_a, K, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, b, (long long)groups * rows_b, K, ldb, bn);
+  if (rc) return rc;
+  const dim3 grid(slots, rows_b / bn);
+  switch (bn) {
+    case 16: return launch_grouped<16>(ma, mb, p, grid, starts, groups, stream);
+    case 32: return launch_grouped<32>(ma, mb, p, grid, starts, groups, stream);
+    case 64: return launch_grouped<64>(ma, mb, p, grid, starts, groups, stream);
+    case 128: return launch_grouped<128>(ma, mb, p, grid, starts, groups, stream);
+    default: return launch_grouped<256>(ma, mb, p, grid, starts, groups, stream);
+  }
+}
 
 // out = A * B^T in the layout the strides give; see the file header.
 //   a: [rows_a, K] bf16, row stride lda;  b: [rows_b, K] bf16, row stride ldb

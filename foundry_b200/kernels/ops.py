@@ -43,6 +43,8 @@ _SIGNATURES = {
                           c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_float, c_void_p],
     "fb_sum_planes": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p],
+    "fb_gemm_tc_grouped": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_int,
+                           c_int, c_void_p, c_ll, c_int, c_void_p],
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
                    c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int,
                    c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_ll, c_void_p,
@@ -71,12 +73,12 @@ _SIGNATURES = {
                              c_float, c_void_p],
     "fb_attention_prefill_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
                                 c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int,
-                                c_int, c_int, c_float, c_void_p],
+                                c_int, c_int, c_float, c_void_p, c_void_p],
     "fb_attention_tc_status": [c_void_p],
     "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_ll, c_int, c_void_p],
+                            c_ll, c_int, c_void_p, c_void_p],
     "fb_gemm_rows": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_int,
                      c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_ll, c_void_p,
                      c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
@@ -1425,13 +1427,28 @@ FAST_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention ke
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
               k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int, num_kv_heads: int,
               head_dim: int, scale: float, window: int = 0, ring_pages: int = 0,
-              then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
+              then_reads: Optional[torch.Tensor] = None,
+              sink_logits: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a step's tokens over the cache: the kernel that fits the
     element type and the step. bfloat16 with a built head size runs on the
     tensor cores (one kernel for single-token steps, one for prompts); float32,
-    windows and other head sizes run on the CUDA cores."""
+    windows and other head sizes run on the CUDA cores. `sink_logits` (float32, one a
+    query head): the softmax's sum has one more term exp(sink_logits[head]) without a key
+    or a value; every tensor-core kernel takes it, elsewhere the CUDA-core kernel of
+    `attention_sink` runs."""
     fast = (q.dtype == torch.bfloat16 and head_dim in FAST_HEAD_DIMS and window == 0
-            and ring_pages == 0 and num_heads // num_kv_heads <= 16)
+            and ring_pages == 0 and num_heads // num_kv_heads <= 16
+            and k_cache.stride() == v_cache.stride())
+    if sink_logits is not None:
+        if tuple(sink_logits.shape) != (num_heads,) or sink_logits.dtype != torch.float32:
+            raise KernelError(f"attention: sink scores {tuple(sink_logits.shape)} "
+                              f"{sink_logits.dtype} for {num_heads} heads")
+        if not fast or ring_pages or window:
+            if ring_pages:
+                raise KernelError("attention: no kernel walks a ring of pages with a sink")
+            return attention_sink(ctx, q, out, page_table, k_cache, v_cache, num_heads,
+                                  num_kv_heads, head_dim, head_dim, scale, window=window,
+                                  sink_logits=sink_logits)
     if not fast:
         return attention_simt(q, out, ctx.positions, ctx.seq_of_token, page_table, k_cache,
                               v_cache, num_heads, num_kv_heads, head_dim, scale, window, ring_pages)
@@ -1441,7 +1458,7 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
                                      getattr(ctx, "unequal_lengths", False))
         return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                                 num_heads, num_kv_heads, head_dim, scale, splits, stages,
-                                then_reads=then_reads)
+                                then_reads=then_reads, sink_logits=sink_logits)
     if ctx.cu_tokens_host is None:
         # a step replayed from a graph: the grid comes from the bucket's bound of
         # 64-row blocks (blocks beyond the real count return at once)
@@ -1453,7 +1470,11 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
                                       sum((n + 127) // 128 for n in lens), max(lens))
     if head_dim in TC_HEAD_DIMS and PREFILL_TC and longest >= 64 and _tc_attention_ok(q, out):
         return attention_prefill_tc(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache,
-                                    v_cache, num_heads, num_kv_heads, head_dim, scale, blocks128)
+                                    v_cache, num_heads, num_kv_heads, head_dim, scale, blocks128,
+                                    sink_logits=sink_logits)
+    if sink_logits is not None:  # the `mma.sync` prompt kernel in its form with a sink
+        return attention_sink(ctx, q, out, page_table, k_cache, v_cache, num_heads, num_kv_heads,
+                              head_dim, head_dim, scale, sink_logits=sink_logits)
     return attention_prefill(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                              num_heads, num_kv_heads, head_dim, scale, blocks)
 
@@ -1502,7 +1523,8 @@ def _tc_attention_ok(q: torch.Tensor, out: torch.Tensor) -> bool:
 
 
 def attention_prefill_tc(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
-                         num_kv_heads, head_dim, scale, q_blocks) -> torch.Tensor:
+                         num_kv_heads, head_dim, scale, q_blocks,
+                         sink_logits: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Prompt attention on tcgen05 (csrc/attention_tcgen05.cu); `q_blocks` is the
     sum over sequences of ceil(tokens / 128)."""
     _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
@@ -1511,7 +1533,8 @@ def attention_prefill_tc(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cach
           _dev(cu_tokens, "cu_tokens", torch.int32), _dev(kv_lens, "kv_lens", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(),
           v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), k_cache.shape[0],
-          kv_lens.numel(), q_blocks, num_heads, num_kv_heads, head_dim, float(scale), _stream())
+          kv_lens.numel(), q_blocks, num_heads, num_kv_heads, head_dim, float(scale),
+          0 if sink_logits is None else _dev(sink_logits, "sink_logits", torch.float32), _stream())
     return out
 
 
@@ -1538,7 +1561,8 @@ DECODE_CLUSTER = _os.environ.get("FOUNDRY_B200_DECODE_CLUSTER", "1") != "0"
 def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
                      num_kv_heads, head_dim, scale, splits, stages: int = 3,
                      then_reads: Optional[torch.Tensor] = None,
-                     cluster: Optional[int] = None) -> torch.Tensor:
+                     cluster: Optional[int] = None,
+                     sink_logits: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core attention for one token per sequence, the cache range split
     over `splits` CTAs per (sequence, kv head). `cluster` of them (by default as
     many as divide `splits`, up to 8) form a thread-block cluster and merge their
@@ -1568,6 +1592,7 @@ def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, n
           0 if ws_o is None else ws_o.data_ptr(), 0 if ws_ml is None else ws_ml.data_ptr(),
           0 if counters is None else counters.data_ptr(), *_prefetch_range(then_reads),
           1 if n > SKINNY_ROWS else 0,  # what follows is a tcgen05 product, not the streaming one
+          0 if sink_logits is None else _dev(sink_logits, "sink_logits", torch.float32),
           _stream())
     return out
 
@@ -2423,6 +2448,38 @@ def moe_grouped(x: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gated: boo
 
 
 MOE_GROUPED_MMA = _os.environ.get("FOUNDRY_B200_MOE_GROUPED_MMA", "1") != "0"
+# Many tokens: every expert's rows through ONE tcgen05 launch a product ("0": a launch
+# per expert through the dense products, which needs the experts' counts on the host)
+MOE_GROUPED_TC = _os.environ.get("FOUNDRY_B200_MOE_GROUPED_TC", "1") != "0"
+
+
+def moe_grouped_tc_fits(x: torch.Tensor, *sizes: int) -> bool:
+    """Whether the grouped tcgen05 product takes the experts' products: bfloat16, and
+    every inner and outer size (`sizes`) in whole 16-element pieces."""
+    return (MOE_GROUPED_TC and x.dtype == torch.bfloat16 and x.is_cuda
+            and all(n % 16 == 0 for n in sizes))
+
+
+def gemm_tc_grouped(rows: torch.Tensor, w: torch.Tensor, order: "ExpertOrder",
+                    out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """out[i] = rows[i] @ w[expert of row i]^T for rows sorted by expert (`order.starts`):
+    rows [pairs, K] bfloat16, w [E, N, K] bfloat16 -> [pairs, N], in one launch on the
+    tensor cores (csrc/gemm_tcgen05.cu, `gemm_tc_grouped_kernel`). Nothing of the launch
+    depends on the experts' counts, so a captured step may hold it."""
+    pairs, K = rows.shape
+    E, N, Kw = w.shape
+    if Kw != K or E != order.experts or pairs != order.pairs or not w.is_contiguous():
+        raise KernelError(f"gemm_tc_grouped: rows {tuple(rows.shape)} for weights {tuple(w.shape)} "
+                          f"of {order.experts} experts and {order.pairs} pairs")
+    if rows.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_grouped takes bfloat16 operands")
+    out = torch.empty((pairs, N), dtype=out_dtype, device=rows.device)
+    if pairs == 0:
+        return out
+    _call("fb_gemm_tc_grouped", _dev(rows, "rows", contiguous=False), _rows(rows, "rows"), pairs,
+          _dev(w, "w"), K, N, K, order.starts.data_ptr(), E, pairs // 128 + E, _dev(out, "out"),
+          N, 1 if out_dtype == torch.float32 else 0, _stream(), tag=("m{} k{} n{}", pairs, K, N))
+    return out
 
 
 def moe_grouped_mma_fits(x: torch.Tensor, *ks: int) -> bool:

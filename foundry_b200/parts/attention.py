@@ -24,7 +24,47 @@ from ..config.spec import PartSpec
 from ..kernels import ops
 from ..weights.loader import ExpectedTensor
 from .base import POSITION_ENCODINGS, Fetch, Part, register_mixer
-from .linear import Linear
+from .linear import Linear, matmul_nt
+
+
+def rotated_projection(ctx, x, weight: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
+                       pairing: str, angles_key, cache: KVView, num_heads: int,
+                       num_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """The fused q | k | v projection of a step (keys and values of one head size), the
+    rotation of queries and keys by `inv_freq` (float32; the angle is a 32-bit product)
+    and the cache write, by the form that fits the step; returns the rotated queries
+    [T, heads * head_dim] in the activation type. `x` may be an `ops.RowScaled`.
+    `angles_key` names the step's shared table of angles in `ctx.shared`."""
+    table = ctx.page_table(cache.group)
+    if ops.qkv_rope_fusable(x, weight, rotary_dim, head_dim, cache.k):
+        # a handful of tokens: projection, rotation and cache write in one kernel
+        return ops.gemm_skinny_rope(x, weight, ctx.positions, ctx.seq_of_token, table, inv_freq,
+                                    rotary_dim, cache.k, cache.v, num_heads, num_kv_heads,
+                                    head_dim, ring_pages=cache.group.ring_pages,
+                                    write_cache=cache.writes, pairing=pairing)
+    if ops.qkv_rows_rope_fusable(x, weight, rotary_dim, head_dim, cache.k, pairing):
+        # up to a few hundred tokens: the same on the tcgen05 product
+        return ops.gemm_rows_rope(x, weight, ctx.positions, ctx.seq_of_token, table, inv_freq,
+                                  rotary_dim, cache.k, cache.v, num_heads, num_kv_heads, head_dim,
+                                  ring_pages=cache.group.ring_pages, write_cache=cache.writes)
+    if ops.qkv_tc_rope_fusable(x, weight, rotary_dim, head_dim, cache.k, pairing):
+        # a prompt: the same in the epilogue of the products whose rows are tokens,
+        # with the step's angles from a table that the first layer of the step makes
+        shared = getattr(ctx, "shared", None)
+        cs = shared.get(angles_key) if shared is not None else None
+        if cs is None:
+            cs = ops.rope_table(ctx.positions, inv_freq)
+            if shared is not None:
+                shared[angles_key] = cs
+        return ops.gemm_tc_rope(x, weight, cs, ctx.positions, ctx.seq_of_token, table, rotary_dim,
+                                cache.k, cache.v, num_heads, num_kv_heads, head_dim,
+                                ring_pages=cache.group.ring_pages, write_cache=cache.writes)
+    # (a row-scaled input stays so: the tcgen05 products apply the scale)
+    qkv = matmul_nt(x, weight, allow_planes=True)  # a tensor or split-K planes
+    return ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, inv_freq, rotary_dim,
+                             cache.k, cache.v, num_heads, num_kv_heads, head_dim,
+                             ring_pages=cache.group.ring_pages, write_cache=cache.writes,
+                             dtype=ops.plain(x).dtype, pairing=pairing)
 
 
 @register_mixer("gqa_attention")
@@ -111,42 +151,9 @@ class GQAAttention(Part):
     # ------------------------------------------------------------------- run
     def forward(self, ctx, x, cache: KVView):
         table = ctx.page_table(cache.group)
-        if ops.qkv_rope_fusable(x, self.qkv.weight, self.rotary_dim, self.head_dim, cache.k):
-            # a handful of tokens: projection, rotation and cache write in one kernel
-            q = ops.gemm_skinny_rope(x, self.qkv.weight, ctx.positions, ctx.seq_of_token, table,
-                                     self.inv_freq, self.rotary_dim, cache.k, cache.v,
-                                     self.num_heads, self.num_kv_heads, self.head_dim,
-                                     ring_pages=cache.group.ring_pages, write_cache=cache.writes,
-                                     pairing=self.pairing)
-        elif ops.qkv_rows_rope_fusable(x, self.qkv.weight, self.rotary_dim, self.head_dim, cache.k,
-                                       self.pairing):
-            # up to a few hundred tokens: the same on the tcgen05 product
-            q = ops.gemm_rows_rope(x, self.qkv.weight, ctx.positions, ctx.seq_of_token, table,
-                                   self.inv_freq, self.rotary_dim, cache.k, cache.v,
-                                   self.num_heads, self.num_kv_heads, self.head_dim,
-                                   ring_pages=cache.group.ring_pages, write_cache=cache.writes)
-        elif ops.qkv_tc_rope_fusable(x, self.qkv.weight, self.rotary_dim, self.head_dim, cache.k,
-                                     self.pairing):
-            # a prompt: the same in the epilogue of the products whose rows are tokens,
-            # with the step's angles from a table that the first layer of the step makes
-            shared = getattr(ctx, "shared", None)
-            cs = shared.get(self.angles_key) if shared is not None else None
-            if cs is None:
-                cs = ops.rope_table(ctx.positions, self.inv_freq)
-                if shared is not None:
-                    shared[self.angles_key] = cs
-            q = ops.gemm_tc_rope(x, self.qkv.weight, cs, ctx.positions, ctx.seq_of_token, table,
-                                 self.rotary_dim, cache.k, cache.v, self.num_heads,
-                                 self.num_kv_heads, self.head_dim,
-                                 ring_pages=cache.group.ring_pages, write_cache=cache.writes)
-        else:
-            # (a row-scaled input stays so: the tcgen05 products apply the scale)
-            qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes
-            q = ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
-                                  self.rotary_dim, cache.k, cache.v, self.num_heads,
-                                  self.num_kv_heads, self.head_dim,
-                                  ring_pages=cache.group.ring_pages, write_cache=cache.writes,
-                                  dtype=x.dtype, pairing=self.pairing)
+        q = rotated_projection(ctx, x, self.qkv.weight, self.inv_freq, self.rotary_dim,
+                               self.pairing, self.angles_key, cache, self.num_heads,
+                               self.num_kv_heads, self.head_dim)
         attn = torch.empty((x.shape[0], self.q_size), dtype=x.dtype, device=x.device)
         ops.attention(ctx, q, attn, table, cache.k, cache.v, self.num_heads, self.num_kv_heads,
                       self.head_dim, self.scale, window=cache.group.window,

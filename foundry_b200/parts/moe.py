@@ -130,7 +130,13 @@ class RoutedExperts(Part):
             return ops.moe_experts_rows(x, self.gate_up, self.down, chosen, weights, out,
                                         self.limit, self.alpha, self.shift, addend=shared)
         order = ops.ExpertOrder(chosen, self.experts)
-        if T >= self.LIBRARY_ROWS and getattr(ctx, "cu_tokens_host", None) is not None:
+        if T >= self.LIBRARY_ROWS and ops.moe_grouped_tc_fits(x, self.width, self.ff):
+            # many tokens: every expert's rows in one tcgen05 launch a product
+            gate_up = ops.gemm_tc_grouped(ops.moe_gather(ops.plain(x), order), self.gate_up, order)
+            act = torch.empty((order.pairs, self.ff), dtype=x.dtype, device=x.device)
+            ops.moe_glu(gate_up, act, order, self.limit, self.alpha, self.shift)
+            y = ops.gemm_tc_grouped(act, self.down, order)
+        elif T >= self.LIBRARY_ROWS and getattr(ctx, "cu_tokens_host", None) is not None:
             y = self._per_expert_products(ops.moe_gather(x, order), order)
         elif ops.moe_grouped_mma_fits(x, self.width, self.ff):
             act = ops.moe_grouped_mma(x, self.gate_up, order, True, self.limit, self.alpha,
@@ -142,9 +148,10 @@ class RoutedExperts(Part):
             y = ops.moe_grouped(act, self.down, order, False)
         return ops.moe_combine(y, order, weights, out, addend=shared)
 
-    # From this many tokens on, a step that is launched plainly (its context has the
-    # host copies; such a step is never captured) runs every expert's rows through
-    # the tensor-core products, which needs the experts' counts on the host.
+    # From this many tokens on the experts' products run on the tcgen05 products: as one
+    # grouped launch a product where the sizes allow it; else, in a step that is launched
+    # plainly (its context has the host copies; such a step is never captured), expert by
+    # expert through the dense products, which needs the experts' counts on the host.
     LIBRARY_ROWS = 128
 
     def _per_expert_products(self, rows, order):

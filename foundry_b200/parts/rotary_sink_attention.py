@@ -15,6 +15,14 @@ values `vdim`. With `own_kv = False` the mixer has no key and value projections:
 reads the cache entry that another run of the schedule wrote (keys as they were rotated
 there), with its own queries, sink and output projection. Tensor names under the
 mixer's prefix: `q k v o sink`.
+
+Kernels. The general path, any sizes and both element types: one product for q | k | v
+(float32 out), one kernel that rotates (the angle a 64-bit product) and writes the cache
+rows, the CUDA-core attention with the sink. In bfloat16, with keys and values of one
+size that the tensor-core attentions have, the mixer runs as the plain grouped attention
+does: rotation and cache write in the projection's epilogue (the angle a 32-bit
+product), the tcgen05 attention for prompts and the split-range `mma.sync` attention for
+single tokens, both with the sink's term as the start of the running sum.
 """
 from __future__ import annotations
 
@@ -26,6 +34,7 @@ import torch
 from ..cache.store import KVRequest, KVView
 from ..kernels import ops
 from ..weights.loader import ExpectedTensor
+from .attention import rotated_projection
 from .base import Fetch, Part, register_mixer
 from .products import product_f32, product_to_residual
 
@@ -52,6 +61,9 @@ class RotarySinkAttention(Part):
         self.dtype, self.device = dtype, device
         self.nq, self.nk, self.nv = heads * dim, kv_heads * dim, kv_heads * vdim
         self.freq = torch.from_numpy(freq.copy()).to(device) if freq.size else None
+        # for the projections that rotate in their epilogue (bfloat16 steps)
+        self.inv_freq = torch.from_numpy(freq.astype(np.float32)).to(device)
+        self.angles_key = ("rotary angles", freq.astype(np.float32).tobytes())
         self.w_in = self.w_o = self.sink_logits = None
 
     def _shapes(self):
@@ -82,11 +94,24 @@ class RotarySinkAttention(Part):
         pairs = sum(0.5 * n * (2 * start + n + 1) for n, start in zip(token_counts, starts))
         return 2.0 * self.heads * (self.dim + self.vdim) * pairs
 
+    def _as_plain_heads(self, x, cache: KVView) -> bool:
+        """Whether the step runs on the kernels of the plain grouped attention."""
+        return (x.dtype == torch.bfloat16 and self.dim == self.vdim
+                and self.dim in ops.FAST_HEAD_DIMS and self.heads // self.kv_heads <= 16
+                and cache.k.stride() == cache.v.stride() and self.pairing == "interleaved")
+
     def forward(self, ctx, x, cache: KVView):
         T = x.shape[0]
         H, G, d, e = self.heads, self.kv_heads, self.dim, self.vdim
         table = ctx.page_table(cache.group)
         writes = self.own_kv and cache.writes
+        if self.own_kv and self._as_plain_heads(x, cache):
+            q = rotated_projection(ctx, x, self.w_in, self.inv_freq, 2 * self.inv_freq.numel(),
+                                   self.pairing, self.angles_key, cache, H, G, d)
+            attn = torch.empty((T, H * e), dtype=x.dtype, device=x.device)
+            ops.attention(ctx, q, attn, table, cache.k, cache.v, H, G, d, self.scale,
+                          then_reads=self.w_o, sink_logits=self.sink_logits)
+            return product_to_residual(ctx, attn, self.w_o)
         rows = product_f32(x, self.w_in)  # [T, q | k | v] or [T, q]
         q = torch.empty((T, self.nq), dtype=x.dtype, device=x.device)
         ops.head_norm_rope_cache_write(rows, q, None, None, 1.0, False, self.freq, ctx.positions,
@@ -94,6 +119,10 @@ class RotarySinkAttention(Part):
                                        G if self.own_kv else 0, d, e, write_cache=writes,
                                        qk_norm=False, pairing=self.pairing)
         attn = torch.empty((T, H * e), dtype=x.dtype, device=x.device)
-        ops.attention_sink(ctx, q, attn, table, cache.k, cache.v, H, G, d, e, self.scale,
-                           sink_logits=self.sink_logits)
+        if self._as_plain_heads(x, cache):  # a reader of another run's keys and values
+            ops.attention(ctx, q, attn, table, cache.k, cache.v, H, G, d, self.scale,
+                          then_reads=self.w_o, sink_logits=self.sink_logits)
+        else:
+            ops.attention_sink(ctx, q, attn, table, cache.k, cache.v, H, G, d, e, self.scale,
+                               sink_logits=self.sink_logits)
         return product_to_residual(ctx, attn, self.w_o)

@@ -1102,3 +1102,31 @@ def _many_rows_norm(ops, M, H, K):
     gu = (pending.values.double() @ pairs.double().T) * rstd
     close(hidden, gu[:, 0::2] / (1 + torch.exp(-gu[:, 0::2])) * gu[:, 1::2], 2e-3, 1e-2)
     assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("sizes", [(64, 48, [0, 1, 128, 129, 300, 0, 7]), (200, 256, [130, 0, 0, 5]),
+                                   (512, 160, [1000, 24]), (72, 16, [3])])
+def test_gemm_tc_grouped(sizes):
+    """The grouped tcgen05 product: groups of no rows, one row, exactly a tile and a tile
+    and a row; K that is no multiple of a K block; tile widths 16 to 256; float32 and
+    bfloat16 outputs. Rows of the next group that a tile reads are not stored."""
+    from foundry_b200.kernels import ops
+    K, N, counts = sizes
+    E, pairs = len(counts), sum(counts)
+    gen = torch.Generator().manual_seed(K + N)
+    rows = torch.randn(pairs, K, generator=gen).to(torch.bfloat16)
+    w = (torch.randn(E, N, K, generator=gen) / K ** 0.5).to(torch.bfloat16)
+    group = torch.repeat_interleave(torch.arange(E), torch.tensor(counts))
+    want = torch.einsum("ik,ink->in", rows.float(), w.float()[group])
+
+    class Order:  # what the sort of the pairs leaves, made by hand
+        experts, starts = E, torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32,
+                                          device="cuda")
+    Order.pairs = pairs
+    for out_dtype, tol in ((torch.float32, 2e-3), (torch.bfloat16, 2e-2)):
+        guard = torch.full((pairs + 256, N), 7.0, dtype=out_dtype, device="cuda")
+        got = ops.gemm_tc_grouped(rows.cuda(), w.cuda(), Order, out_dtype)
+        torch.cuda.synchronize()
+        ops.raise_on_device_failure()
+        assert torch.allclose(got.float().cpu(), want, rtol=tol, atol=tol), (sizes, out_dtype)
+        assert bool((guard == 7.0).all())
