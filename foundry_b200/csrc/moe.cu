@@ -22,21 +22,17 @@
 
 namespace {
 
-__global__ void moe_route_kernel(const float* z, long long ld, const float* __restrict__ bias,
-                                 int E, int top, int* __restrict__ chosen,
-                                 float* __restrict__ weights, int score, int groups, int keep,
-                                 const float* __restrict__ correction, int normalise,
-                                 float sum_floor, float weight_scale) {
-  fb_pdl_launch();
-  fb_pdl_wait();
-  // one warp per token; each lane keeps the experts lane, lane + 32, ... (up to 8 of them).
+// One token's choice, by one warp. s_all, s_group, s_plain: 256 floats each of this warp's own.
+__device__ __forceinline__ void route_token(const float* z, long long ld,
+                                            const float* __restrict__ bias, int E, int top,
+                                            int* __restrict__ chosen, float* __restrict__ weights,
+                                            int score, int groups, int keep,
+                                            const float* __restrict__ correction, int normalise,
+                                            float sum_floor, float weight_scale, int t, int lane,
+                                            float* s_all, float* s_group, float* s_plain) {
+  // each lane keeps the experts lane, lane + 32, ... (up to 8 of them).
   // v[] is what the choice goes by (the score, plus `correction` where given); the
   // weights come from the scores themselves (s_plain).
-  __shared__ float s_all[256];
-  __shared__ float s_group[256];
-  __shared__ float s_plain[256];
-  const int t = blockIdx.x;
-  const int lane = threadIdx.x & 31;
   float v[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -118,6 +114,22 @@ __global__ void moe_route_kernel(const float* z, long long ld, const float* __re
     weights[(size_t)t * top + lane] =
         score == 1 ? (normalise ? mine / (sum + sum_floor) * weight_scale : mine * weight_scale)
                    : mine / sum;
+  __syncwarp();  // a warp that goes on to another token writes the shared tables again
+}
+
+__global__ void moe_route_kernel(const float* z, long long ld, const float* __restrict__ bias,
+                                 int E, int top, int* __restrict__ chosen,
+                                 float* __restrict__ weights, int score, int groups, int keep,
+                                 const float* __restrict__ correction, int normalise,
+                                 float sum_floor, float weight_scale) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  // one warp per token
+  __shared__ float s_all[256];
+  __shared__ float s_group[256];
+  __shared__ float s_plain[256];
+  route_token(z, ld, bias, E, top, chosen, weights, score, groups, keep, correction, normalise,
+              sum_floor, weight_scale, blockIdx.x, threadIdx.x & 31, s_all, s_group, s_plain);
 }
 
 template <typename T>
@@ -258,10 +270,9 @@ FB_API int fb_moe_experts_rows(const void* h, int dtype, const void* gate_up, co
 //                     order of c, so the sum does not depend on the sorting
 namespace {
 
-__global__ void moe_sort_kernel(const int* chosen, int n_pairs, int E, int* __restrict__ counts,
-                                int* __restrict__ starts, int* __restrict__ place,
-                                int* __restrict__ pair_at) {
-  fb_pdl_wait();
+__device__ __forceinline__ void sort_pairs(const int* chosen, int n_pairs, int E,
+                                           int* __restrict__ counts, int* __restrict__ starts,
+                                           int* __restrict__ place, int* __restrict__ pair_at) {
   // one block; counts and starts live in shared memory (E <= 256)
   __shared__ int cnt[256], start[257];
   for (int e = threadIdx.x; e < 256; e += blockDim.x) cnt[e] = 0;
@@ -301,6 +312,36 @@ __global__ void moe_sort_kernel(const int* chosen, int n_pairs, int E, int* __re
     const int e = chosen[i];
     if (e < 0 || e >= E) place[i] = -1;
   }
+}
+
+__global__ void moe_sort_kernel(const int* chosen, int n_pairs, int E, int* __restrict__ counts,
+                                int* __restrict__ starts, int* __restrict__ place,
+                                int* __restrict__ pair_at) {
+  fb_pdl_wait();
+  sort_pairs(chosen, n_pairs, E, counts, starts, place, pair_at);
+}
+
+// Choice and sort in one block, for the few tokens of a single-token step: eight warps
+// take the tokens in turn, then the block sorts the pairs it has just written.
+constexpr int ROUTE_SORT_WARPS = 8;
+__global__ void __launch_bounds__(ROUTE_SORT_WARPS * 32)
+moe_route_sort_kernel(const float* z, long long ld, const float* __restrict__ bias, int E, int top,
+                      int* chosen, float* __restrict__ weights, int score, int groups, int keep,
+                      const float* __restrict__ correction, int normalise, float sum_floor,
+                      float weight_scale, int T, int* __restrict__ counts,
+                      int* __restrict__ starts, int* __restrict__ place,
+                      int* __restrict__ pair_at) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  __shared__ float s_all[ROUTE_SORT_WARPS][256];
+  __shared__ float s_group[ROUTE_SORT_WARPS][256];
+  __shared__ float s_plain[ROUTE_SORT_WARPS][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int t = warp; t < T; t += ROUTE_SORT_WARPS)
+    route_token(z, ld, bias, E, top, chosen, weights, score, groups, keep, correction, normalise,
+                sum_floor, weight_scale, t, lane, s_all[warp], s_group[warp], s_plain[warp]);
+  __syncthreads();  // the block's own writes of `chosen` are visible to all its threads
+  sort_pairs(chosen, T * top, E, counts, starts, place, pair_at);
 }
 
 template <typename T>
@@ -579,6 +620,28 @@ FB_API int fb_moe_sort(const int* chosen, int n_pairs, int E, int* counts, int* 
   fb_launch(moe_sort_kernel, dim3(1), dim3(256), 0, stream, chosen, n_pairs, E, counts, starts,
             place, pair_at);
   return fb_check_launch("moe_sort");
+}
+
+// fb_moe_route and fb_moe_sort as one launch of one block (for up to a few dozen tokens).
+FB_API int fb_moe_route_sort(const float* z, long long ld, const float* bias, int E, int top,
+                             int* chosen, float* weights, int T, int score, int groups, int keep,
+                             const float* correction, int normalise, float sum_floor,
+                             float weight_scale, int* counts, int* starts, int* place,
+                             int* pair_at, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && E > 0 && E <= 256 && top > 0 && top <= E && top <= 32 && ld >= E,
+             "moe_route_sort: %d experts (at most 256), %d chosen (at most 32)", E, top);
+  FB_REQUIRE(score == 0 || score == 1, "moe_route_sort: unknown scoring rule %d", score);
+  FB_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups &&
+             (long long)keep * (E / groups) >= top,
+             "moe_route_sort: %d groups of %d experts, %d kept, %d chosen", groups, E, keep, top);
+  FB_REQUIRE(score == 1 || (groups == 1 && correction == nullptr && !normalise &&
+                            weight_scale == 1.0f),
+             "moe_route_sort: groups, a correction, shares of the sum and a constant on the "
+             "weights need the sigmoid scores");
+  fb_launch(moe_route_sort_kernel, dim3(1), dim3(ROUTE_SORT_WARPS * 32), 0, stream, z, ld, bias, E,
+            top, chosen, weights, score, groups, keep, correction, normalise, sum_floor,
+            weight_scale, T, counts, starts, place, pair_at);
+  return fb_check_launch("moe_route_sort");
 }
 
 FB_API int fb_moe_gather(const void* x, int dtype, const int* pair_at, const int* starts, int E,

@@ -160,6 +160,9 @@ _SIGNATURES = {
     "fb_unary_cast": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "fb_add_into": [c_void_p, c_void_p, c_ll, c_void_p],
     "fb_sigmoid_gate": [c_void_p, c_int, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p],
+    "fb_moe_route_sort": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                          c_int, c_int, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p,
+                          c_void_p, c_void_p, c_void_p],
     "fb_moe_route": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                      c_int, c_void_p, c_int, c_float, c_float, c_void_p],
     "fb_moe_experts_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -2386,7 +2389,7 @@ class ExpertOrder:
     `starts` [E + 1] running sums of the experts' pair counts, `place` [T, top]
     each pair's row in the sorted order (-1: none), `pair_at` the inverse."""
 
-    def __init__(self, chosen: torch.Tensor, experts: int):
+    def __init__(self, chosen: torch.Tensor, experts: int, sort: bool = True):
         T, top = chosen.shape
         dev = chosen.device
         self.T, self.top, self.experts, self.pairs = T, top, experts, T * top
@@ -2394,9 +2397,40 @@ class ExpertOrder:
         self.starts = torch.empty(experts + 1, dtype=torch.int32, device=dev)
         self.place = torch.empty((T, top), dtype=torch.int32, device=dev)
         self.pair_at = torch.empty(T * top, dtype=torch.int32, device=dev)
+        if not sort:  # whoever made the choice fills the tables itself
+            return
         _call("fb_moe_sort", _dev(chosen, "chosen", torch.int32), self.pairs, experts,
               self.counts.data_ptr(), self.starts.data_ptr(), self.place.data_ptr(),
               self.pair_at.data_ptr(), _stream())
+
+
+# Tokens up to which the choice and the sort of the pairs are one launch of one block
+MOE_ROUTE_SORT_ROWS = int(_os.environ.get("FOUNDRY_B200_MOE_ROUTE_SORT_ROWS", "64"))
+
+
+def moe_route_sorted(z: torch.Tensor, bias: Optional[torch.Tensor], top: int, chosen: torch.Tensor,
+                     weights: torch.Tensor, score: str = "softmax_chosen", groups: int = 1,
+                     keep: int = 1, correction: Optional[torch.Tensor] = None,
+                     normalise: bool = False, sum_floor: float = 0.0,
+                     weight_scale: float = 1.0) -> ExpertOrder:
+    """`moe_route` and the sort of the chosen pairs by expert: for up to
+    `MOE_ROUTE_SORT_ROWS` tokens one launch of one block, else the two kernels."""
+    T, E = z.shape
+    if not 0 < T <= MOE_ROUTE_SORT_ROWS:
+        moe_route(z, bias, top, chosen, weights, score, groups, keep, correction, normalise,
+                  sum_floor, weight_scale)
+        return ExpertOrder(chosen, E)
+    if correction is not None and tuple(correction.shape) != (E,):
+        raise KernelError(f"moe_route: a correction of {tuple(correction.shape)} for {E} experts")
+    order = ExpertOrder(chosen, E, sort=False)
+    _call("fb_moe_route_sort", _dev(z, "z", torch.float32, contiguous=False), _rows(z, "z"),
+          0 if bias is None else _dev(bias, "bias", torch.float32), E, top,
+          _dev(chosen, "chosen", torch.int32), _dev(weights, "weights", torch.float32), T,
+          MOE_SCORES[score], int(groups), int(keep),
+          0 if correction is None else _dev(correction, "correction", torch.float32),
+          1 if normalise else 0, float(sum_floor), float(weight_scale), order.counts.data_ptr(),
+          order.starts.data_ptr(), order.place.data_ptr(), order.pair_at.data_ptr(), _stream())
+    return order
 
 
 def moe_gather(x: torch.Tensor, order: ExpertOrder) -> torch.Tensor:

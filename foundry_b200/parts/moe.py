@@ -115,9 +115,14 @@ class RoutedExperts(Part):
         z = product_f32(x, self.router)
         chosen = torch.empty((T, self.top), dtype=torch.int32, device=x.device)
         weights = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
-        ops.moe_route(z, self.router_bias, self.top, chosen, weights, self.score, self.groups,
-                      self.keep, correction=self.correction, normalise=self.normalise,
-                      sum_floor=self.sum_floor, weight_scale=self.weight_scale)
+        rule = dict(score=self.score, groups=self.groups, keep=self.keep,
+                    correction=self.correction, normalise=self.normalise,
+                    sum_floor=self.sum_floor, weight_scale=self.weight_scale)
+        grouped = ops.moe_grouped_fits(self.width) and ops.moe_grouped_fits(self.ff)
+        if grouped:  # the choice, and the pairs sorted by expert
+            order = ops.moe_route_sorted(z, self.router_bias, self.top, chosen, weights, **rule)
+        else:
+            ops.moe_route(z, self.router_bias, self.top, chosen, weights, **rule)
         # the shared expert's rows join the sum where the chosen experts' rows are combined
         shared = addend
         if self.shared is not None:
@@ -125,11 +130,10 @@ class RoutedExperts(Part):
             if addend is not None:
                 ops.add_into(shared, addend)
         out = torch.empty((T, self.width), dtype=torch.float32, device=x.device)
-        if not (ops.moe_grouped_fits(self.width) and ops.moe_grouped_fits(self.ff)):
+        if not grouped:
             # sizes the grouped kernels do not take: every token streams its own experts
             return ops.moe_experts_rows(x, self.gate_up, self.down, chosen, weights, out,
                                         self.limit, self.alpha, self.shift, addend=shared)
-        order = ops.ExpertOrder(chosen, self.experts)
         if T >= self.LIBRARY_ROWS and ops.moe_grouped_tc_fits(x, self.width, self.ff):
             # many tokens: every expert's rows in one tcgen05 launch a product
             gate_up = ops.gemm_tc_grouped(ops.moe_gather(ops.plain(x), order), self.gate_up, order)

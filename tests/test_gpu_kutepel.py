@@ -245,6 +245,34 @@ def test_the_router_chooses_and_weighs_as_the_plain_one(router):
     assert torch.allclose(weights.cpu().double(), want_weights, rtol=2e-6, atol=1e-7)
 
 
+@pytest.mark.parametrize("router", ROUTERS)
+def test_choice_and_sort_in_one_launch_equal_the_two_kernels(router):
+    """For the few tokens of a single-token step the choice and the sort of the pairs by
+    expert are one launch of one block: the same choice, weights and tables as the two
+    kernels, at 1, 9 and 64 tokens (a warp takes several tokens in turn)."""
+    from foundry_b200.kernels import ops
+    E, top = router["experts"], router["top"]
+    groups = router.get("groups") or {"count": 1, "keep": 1}
+    gen = torch.Generator().manual_seed(E + top)
+    correction = (0.8 * torch.randn(E, generator=gen) - 0.5).to(DEV)
+    rule = dict(score="sigmoid", groups=groups["count"], keep=groups["keep"], correction=correction,
+                normalise=True, sum_floor=plain.WEIGHT_SUM_FLOOR, weight_scale=router["scale"])
+    for T in (1, 9, 64):
+        assert T <= ops.MOE_ROUTE_SORT_ROWS
+        z = (2.0 * torch.randn(T, E, generator=gen)).to(DEV)
+        one = [torch.empty((T, top), dtype=torch.int32, device=DEV),
+               torch.empty((T, top), dtype=torch.float32, device=DEV)]
+        two = [torch.empty_like(one[0]), torch.empty_like(one[1])]
+        fused = ops.moe_route_sorted(z, None, top, one[0], one[1], **rule)
+        ops.moe_route(z, None, top, two[0], two[1], **rule)
+        apart = ops.ExpertOrder(two[0], E)
+        assert torch.equal(one[0], two[0]) and torch.equal(one[1], two[1])
+        for field in ("counts", "starts", "place", "pair_at"):
+            assert torch.equal(getattr(fused, field), getattr(apart, field)), (T, field)
+        want_chosen, _ = plain.route(router, z.double().cpu(), correction.double().cpu())
+        assert one[0].cpu().tolist() == want_chosen.tolist()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", list(tiny.CONFIGS))
 def test_routed_experts_alone_and_beside_an_addend(name, dtype):
