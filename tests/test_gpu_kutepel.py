@@ -608,11 +608,13 @@ def test_long_decoding_and_reused_slots(name, folders):
     assert np.array_equal(first, again)
 
 
-def test_sizes_that_fit_no_tensor_core_product(tmp_path):
-    """Width 52 and inner sizes that are no multiples of 8: in bfloat16 every product takes
-    the CUDA-core kernel and the experts the form that streams a token's own experts."""
+@pytest.mark.parametrize("width", [52, 100])
+def test_sizes_that_fit_no_tensor_core_product(width, tmp_path):
+    """Widths 52 and 100 (the latter long enough for a tensor-core K block, and no whole
+    16-byte pieces) and inner sizes that are no multiples of 8: in bfloat16 every product
+    takes the CUDA-core kernel and the experts the form that streams a token's own experts."""
     import foundry_b200 as fb
-    doc = {"architecture": "Kutepel", "vocab": 77, "width": 52, "norm": {"eps": 1e-5},
+    doc = {"architecture": "Kutepel", "vocab": 77, "width": width, "norm": {"eps": 1e-5},
            "residual_mult": 0.25,
            "layers": [
                {"type": "attention",
