@@ -204,11 +204,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // a CTA beyond the last tile returns at once. A group's last tile also reads the
 // next group's first rows (or zeros behind the last row); those rows of the
 // accumulator are not stored.
-template <int BN>
+//
+// GLU: a group's B holds `rows_b / 2` gate rows and then as many up rows, and the result
+// is act(gate) * up: a tile's B is loaded as two halves (BN / 2 gate rows, and the up rows
+// of the same features), so that a thread of the epilogue finds a feature's two sums in
+// its own row of the accumulator, BN / 2 columns apart, and stores
+//   min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift)
+// in bfloat16 (out [rows, rows_b / 2]). `map_b`'s box is then BN / 2 rows.
+struct GluRule {
+  float limit, alpha, shift;
+};
+
+template <int BN, bool GLU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_b, const GemmParams p,
-                       const int* starts, int groups) {
+                       const int* starts, int groups, const GluRule glu) {
   constexpr int STAGES = Smem<BN>::STAGES;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   extern __shared__ uint8_t smem_raw[];
@@ -259,7 +270,9 @@ gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int b_row = group * p.rows_b + tile_b * BN;  // first row of this tile in the stacked B
+  // first row of this tile in the stacked B (GLU: of its gate rows; the up rows of the
+  // same features lie half a group further)
+  const int b_row = group * p.rows_b + tile_b * (GLU ? BN / 2 : BN);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -272,7 +285,12 @@ gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a,
         uint8_t* b_dst = a_dst + Smem<BN>::A_BYTES;
         mbar_expect_tx(&full[s], Smem<BN>::STAGE_BYTES);
         tma_load_2d(a_dst, &map_a, &full[s], i * BK, row0);
-        tma_load_2d(b_dst, &map_b, &full[s], i * BK, b_row);
+        if constexpr (GLU) {
+          tma_load_2d(b_dst, &map_b, &full[s], i * BK, b_row);
+          tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b, &full[s], i * BK, b_row + p.rows_b / 2);
+        } else {
+          tma_load_2d(b_dst, &map_b, &full[s], i * BK, b_row);
+        }
       }
     }
   } else if (warp == 1) {
@@ -304,29 +322,67 @@ gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a,
     const bool ok = mbar_wait(acc_full, 0, abort_flag, 3, 0);
     tc_fence_after();
     if (ok) {
-      GemmParams mine = p;      // rows of the next group are beyond this tile's bound
-      mine.rows_a = row_end;
-      float* out_f = (float*)p.out;
-      __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
-      constexpr int CHUNK = (BN % 32 == 0) ? 32 : 16;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      if constexpr (GLU) {
+        constexpr int HALF = BN / 2;
+        constexpr int CHUNK = (HALF % 32 == 0) ? 32 : 16;
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + i_global * p.stride_a + (long long)tile_b * HALF;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += CHUNK) {
-        float v[CHUNK];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
-        if constexpr (CHUNK == 32) {
-          uint32_t r[32];
-          tmem_ld32(taddr, r);
+        for (int c = 0; c < HALF; c += CHUNK) {
+          uint32_t g[CHUNK], u[CHUNK];
+          if constexpr (CHUNK == 32) {
+            tmem_ld32(lane_addr + (uint32_t)c, g);
+            tmem_ld32(lane_addr + (uint32_t)(HALF + c), u);
+          } else {
+            tmem_ld16(lane_addr + (uint32_t)c, g);
+            tmem_ld16(lane_addr + (uint32_t)(HALF + c), u);
+          }
           tmem_ld_wait();
+          if (i_global < row_end) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
-        } else {
-          uint32_t r[16];
-          tmem_ld16(taddr, r);
-          tmem_ld_wait();
+            for (int e = 0; e < CHUNK; e += 8) {
+              uint32_t pk[4];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
+              for (int q = 0; q < 4; ++q) {
+                float r2[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const float gate = fminf(__uint_as_float(g[e + 2 * q + h]), glu.limit);
+                  const float up =
+                      fminf(fmaxf(__uint_as_float(u[e + 2 * q + h]), -glu.limit), glu.limit);
+                  r2[h] = gate * (1.0f / (1.0f + __expf(-glu.alpha * gate))) * (up + glu.shift);
+                }
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(r2[0], r2[1]);
+                pk[q] = *reinterpret_cast<const uint32_t*>(&h2);
+              }
+              *reinterpret_cast<uint4*>(dst + c + e) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
         }
-        store_chunk<CHUNK>(mine, v, i_global, (long long)tile_b * BN + c, lane, out_f, out_h);
+      } else {
+        GemmParams mine = p;      // rows of the next group are beyond this tile's bound
+        mine.rows_a = row_end;
+        float* out_f = (float*)p.out;
+        __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
+        constexpr int CHUNK = (BN % 32 == 0) ? 32 : 16;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CHUNK) {
+          float v[CHUNK];
+          if constexpr (CHUNK == 32) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + (uint32_t)c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+          } else {
+            uint32_t r[16];
+            tmem_ld16(lane_addr + (uint32_t)c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
+          }
+          store_chunk<CHUNK>(mine, v, i_global, (long long)tile_b * BN + c, lane, out_f, out_h);
+        }
       }
     }
   }
@@ -556,18 +612,18 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
 }  // namespace
 
 namespace {
-template <int BN>
+template <int BN, bool GLU>
 int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
-                   const int* starts, int groups, cudaStream_t stream) {
+                   const int* starts, int groups, const GluRule& glu, cudaStream_t stream) {
   static bool configured[64] = {};
   if (fb_first_use_on_device(configured)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_grouped_kernel<BN>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_grouped_kernel<BN, GLU>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Smem<BN>::BYTES);
     if (e != cudaSuccess) return fb_fail(2, "gemm_tc_grouped: shared memory opt-in: %s", cudaGetErrorString(e));
   }
-  fb_launch(gemm_tc_grouped_kernel<BN>, grid, dim3(THREADS), Smem<BN>::BYTES, stream, ma, mb, p,
-            starts, groups);
+  fb_launch(gemm_tc_grouped_kernel<BN, GLU>, grid, dim3(THREADS), Smem<BN>::BYTES, stream, ma, mb,
+            p, starts, groups, glu);
   return fb_check_launch("gemm_tc_grouped");
 }
 }  // namespace
@@ -577,39 +633,55 @@ int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParam
 // rows_a), b [groups * rows_b, K] bf16 (the groups' matrices stacked);
 // out[i * ldo + j], float32 (out_f32) or bf16, j < rows_b. `slots`: at least the sum
 // over groups of ceil(rows of the group / 128); rows_a / 128 + groups always is.
+// glu 1: a group's rows are rows_b / 2 gate rows, then as many up rows; out is bf16
+// [rows_a, rows_b / 2] = act(gate) * up with the rule of `gemm_tc_grouped_kernel`.
 FB_API int fb_gemm_tc_grouped(const void* a, long long lda, int rows_a, const void* b,
                               long long ldb, int rows_b, int K, const int* starts, int groups,
-                              int slots, void* out, long long ldo, int out_f32,
-                              cudaStream_t stream) {
+                              int slots, void* out, long long ldo, int out_f32, int glu,
+                              float limit, float alpha, float shift, cudaStream_t stream) {
   FB_REQUIRE(rows_a > 0 && rows_b > 0 && K > 0 && groups > 0 && slots > 0 && starts != nullptr,
              "gemm_tc_grouped: bad sizes %d x %d x %d in %d groups", rows_a, rows_b, K, groups);
   FB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
                  ((uintptr_t)b % 16) == 0,
              "gemm_tc_grouped: K, the row strides and the operands must keep 16-byte alignment");
-  FB_REQUIRE(rows_b % 16 == 0 && ldo >= rows_b, "gemm_tc_grouped: %d features a group (a multiple "
-             "of 16) in rows of %lld", rows_b, ldo);
+  const int features = glu ? rows_b / 2 : rows_b;  // columns of the output
+  FB_REQUIRE(features % 16 == 0 && ldo >= features && (!glu || rows_b % 2 == 0),
+             "gemm_tc_grouped: %d features a group (a multiple of 16) in rows of %lld", features,
+             ldo);
+  FB_REQUIRE(!glu || (!out_f32 && ldo % 8 == 0 && ((uintptr_t)out % 16) == 0),
+             "gemm_tc_grouped: the gated form writes bfloat16 rows on 16-byte boundaries");
   bind_status_mirror(stream);
   // the widest tile that divides a group's features: a tile never spans two groups
+  // (gated: a tile is BN / 2 features wide, their gate rows and their up rows)
   int bn = 256;
-  while (rows_b % bn) bn >>= 1;
+  while (features % (glu ? bn / 2 : bn)) bn >>= 1;
   GemmParams p{};
   p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
   p.kblocks_per_split = (K + BK - 1) / BK;
   p.stride_a = ldo; p.stride_b = 1; p.split_stride = 0;
   p.out = out; p.out_f32 = out_f32; p.epilogue = 0; p.glu_act = 0; p.constant_operand = 2;
   p.full_tiles = 0; p.tail_splits = 1; p.tail_kblocks = p.kblocks_per_split;
+  const GluRule rule{limit, alpha, shift};
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, rows_a, K, lda, BM);
   if (rc) return rc;
-  rc = make_map(&mb, b, (long long)groups * rows_b, K, ldb, bn);
+  rc = make_map(&mb, b, (long long)groups * rows_b, K, ldb, glu ? bn / 2 : bn);
   if (rc) return rc;
   const dim3 grid(slots, rows_b / bn);
+  if (glu) {
+    switch (bn) {
+      case 32: return launch_grouped<32, true>(ma, mb, p, grid, starts, groups, rule, stream);
+      case 64: return launch_grouped<64, true>(ma, mb, p, grid, starts, groups, rule, stream);
+      case 128: return launch_grouped<128, true>(ma, mb, p, grid, starts, groups, rule, stream);
+      default: return launch_grouped<256, true>(ma, mb, p, grid, starts, groups, rule, stream);
+    }
+  }
   switch (bn) {
-    case 16: return launch_grouped<16>(ma, mb, p, grid, starts, groups, stream);
-    case 32: return launch_grouped<32>(ma, mb, p, grid, starts, groups, stream);
-    case 64: return launch_grouped<64>(ma, mb, p, grid, starts, groups, stream);
-    case 128: return launch_grouped<128>(ma, mb, p, grid, starts, groups, stream);
-    default: return launch_grouped<256>(ma, mb, p, grid, starts, groups, stream);
+    case 16: return launch_grouped<16, false>(ma, mb, p, grid, starts, groups, rule, stream);
+    case 32: return launch_grouped<32, false>(ma, mb, p, grid, starts, groups, rule, stream);
+    case 64: return launch_grouped<64, false>(ma, mb, p, grid, starts, groups, rule, stream);
+    case 128: return launch_grouped<128, false>(ma, mb, p, grid, starts, groups, rule, stream);
+    default: return launch_grouped<256, false>(ma, mb, p, grid, starts, groups, rule, stream);
   }
 }
 

@@ -44,7 +44,8 @@ _SIGNATURES = {
                           c_int, c_float, c_void_p],
     "fb_sum_planes": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p],
     "fb_gemm_tc_grouped": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_int,
-                           c_int, c_void_p, c_ll, c_int, c_void_p],
+                           c_int, c_void_p, c_ll, c_int, c_int, c_float, c_float, c_float,
+                           c_void_p],
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
                    c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int,
                    c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_ll, c_void_p,
@@ -2489,17 +2490,22 @@ MOE_GROUPED_TC = _os.environ.get("FOUNDRY_B200_MOE_GROUPED_TC", "1") != "0"
 
 def moe_grouped_tc_fits(x: torch.Tensor, *sizes: int) -> bool:
     """Whether the grouped tcgen05 product takes the experts' products: bfloat16, and
-    every inner and outer size (`sizes`) in whole 16-element pieces."""
+    every inner and outer size (`sizes`) a multiple of 32 (the gated form's tiles hold
+    16 features' gate rows and their up rows at least)."""
     return (MOE_GROUPED_TC and x.dtype == torch.bfloat16 and x.is_cuda
-            and all(n % 16 == 0 for n in sizes))
+            and all(n % 32 == 0 for n in sizes))
 
 
 def gemm_tc_grouped(rows: torch.Tensor, w: torch.Tensor, order: "ExpertOrder",
-                    out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                    out_dtype: torch.dtype = torch.float32,
+                    glu: Optional[tuple] = None) -> torch.Tensor:
     """out[i] = rows[i] @ w[expert of row i]^T for rows sorted by expert (`order.starts`):
     rows [pairs, K] bfloat16, w [E, N, K] bfloat16 -> [pairs, N], in one launch on the
     tensor cores (csrc/gemm_tcgen05.cu, `gemm_tc_grouped_kernel`). Nothing of the launch
-    depends on the experts' counts, so a captured step may hold it."""
+    depends on the experts' counts, so a captured step may hold it. `glu` = (limit, alpha,
+    shift): an expert's rows are N / 2 gate rows and then as many up rows, and the result is
+    bfloat16 [pairs, N / 2] = min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, +-limit) +
+    shift), made in the product's epilogue."""
     pairs, K = rows.shape
     E, N, Kw = w.shape
     if Kw != K or E != order.experts or pairs != order.pairs or not w.is_contiguous():
@@ -2507,12 +2513,17 @@ def gemm_tc_grouped(rows: torch.Tensor, w: torch.Tensor, order: "ExpertOrder",
                           f"of {order.experts} experts and {order.pairs} pairs")
     if rows.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc_grouped takes bfloat16 operands")
-    out = torch.empty((pairs, N), dtype=out_dtype, device=rows.device)
+    if glu is not None:
+        out_dtype = torch.bfloat16
+    width = N // 2 if glu is not None else N
+    out = torch.empty((pairs, width), dtype=out_dtype, device=rows.device)
     if pairs == 0:
         return out
+    limit, alpha, shift = glu if glu is not None else (0.0, 0.0, 0.0)
     _call("fb_gemm_tc_grouped", _dev(rows, "rows", contiguous=False), _rows(rows, "rows"), pairs,
           _dev(w, "w"), K, N, K, order.starts.data_ptr(), E, pairs // 128 + E, _dev(out, "out"),
-          N, 1 if out_dtype == torch.float32 else 0, _stream(), tag=("m{} k{} n{}", pairs, K, N))
+          width, 1 if out_dtype == torch.float32 else 0, 0 if glu is None else 1, float(limit),
+          float(alpha), float(shift), _stream(), tag=("m{} k{} n{}", pairs, K, N))
     return out
 
 

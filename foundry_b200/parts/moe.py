@@ -136,9 +136,9 @@ class RoutedExperts(Part):
                                         self.limit, self.alpha, self.shift, addend=shared)
         if T >= self.LIBRARY_ROWS and ops.moe_grouped_tc_fits(x, self.width, self.ff):
             # many tokens: every expert's rows in one tcgen05 launch a product
-            gate_up = ops.gemm_tc_grouped(ops.moe_gather(ops.plain(x), order), self.gate_up, order)
-            act = torch.empty((order.pairs, self.ff), dtype=x.dtype, device=x.device)
-            ops.moe_glu(gate_up, act, order, self.limit, self.alpha, self.shift)
+            # (the activation is the first product's epilogue)
+            act = ops.gemm_tc_grouped(ops.moe_gather(ops.plain(x), order), self.gate_up, order,
+                                      glu=(self.limit, self.alpha, self.shift))
             y = ops.gemm_tc_grouped(act, self.down, order)
         elif T >= self.LIBRARY_ROWS and getattr(ctx, "cu_tokens_host", None) is not None:
             y = self._per_expert_products(ops.moe_gather(x, order), order)

@@ -1105,7 +1105,8 @@ def _many_rows_norm(ops, M, H, K):
 
 
 @pytest.mark.parametrize("sizes", [(64, 48, [0, 1, 128, 129, 300, 0, 7]), (200, 256, [130, 0, 0, 5]),
-                                   (512, 160, [1000, 24]), (72, 16, [3])])
+                                   (512, 160, [1000, 24]), (72, 16, [3]), (128, 512, [5, 260, 0, 1]),
+                                   (96, 96, [129, 127]), (64, 64, [40])])
 def test_gemm_tc_grouped(sizes):
     """The grouped tcgen05 product: groups of no rows, one row, exactly a tile and a tile
     and a row; K that is no multiple of a K block; tile widths 16 to 256; float32 and
@@ -1130,3 +1131,14 @@ def test_gemm_tc_grouped(sizes):
         ops.raise_on_device_failure()
         assert torch.allclose(got.float().cpu(), want, rtol=tol, atol=tol), (sizes, out_dtype)
         assert bool((guard == 7.0).all())
+    if N % 32 == 0:
+        # the gated form: a group's rows are N / 2 gate rows and then as many up rows
+        for limit, alpha, shift in ((float("inf"), 1.0, 0.0), (0.8, 1.702, 1.0)):
+            g, u = want[:, :N // 2], want[:, N // 2:]
+            gc, uc = g.clamp(max=limit), u.clamp(-limit, limit)
+            act = gc * torch.sigmoid(alpha * gc) * (uc + shift)
+            got = ops.gemm_tc_grouped(rows.cuda(), w.cuda(), Order, glu=(limit, alpha, shift))
+            torch.cuda.synchronize()
+            ops.raise_on_device_failure()
+            assert got.dtype == torch.bfloat16 and tuple(got.shape) == (pairs, N // 2)
+            assert torch.allclose(got.float().cpu(), act, rtol=2e-2, atol=2e-2), (sizes, limit)
