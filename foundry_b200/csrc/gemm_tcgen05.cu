@@ -397,6 +397,231 @@ gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
+// The grouped product as one CTA per SM that walks over the tiles, with two accumulators in
+// tensor memory as in the persistent dense product below: the epilogue of tile j runs while
+// the products of tile j + 1 are issued, and the loads run ahead of both. The CTA first
+// turns `starts` into a table of row tiles in shared memory (slot -> group, first row, end
+// of the group's rows); a tile is (slot, B tile) with the slot running fastest, so that the
+// row tiles of one group meet the same weights in neighbouring CTAs.
+constexpr int GROUPED_MAX_SLOTS = 1024;
+
+template <int BN, bool GLU>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_grouped_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                  const __grid_constant__ CUtensorMap map_b, const GemmParams p,
+                                  const int* starts, int groups, const GluRule glu, int tiles_b) {
+  constexpr int STAGES = Smem<BN>::STAGES;
+  constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * Smem<BN>::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  __shared__ int s_starts[257];
+  __shared__ int s_group[GROUPED_MAX_SLOTS], s_row0[GROUPED_MAX_SLOTS], s_end[GROUPED_MAX_SLOTS];
+  __shared__ int s_slots;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (p.K + BK - 1) / BK;
+
+  // `starts` is the work of an earlier kernel: nothing is known before the wait
+  fb_pdl_wait();
+  for (int g = threadIdx.x; g <= groups; g += blockDim.x) s_starts[g] = __ldcg(starts + g);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int g = 0; g < groups; ++g)
+      for (int r = s_starts[g]; r < s_starts[g + 1] && n < GROUPED_MAX_SLOTS; r += BM, ++n) {
+        s_group[n] = g;
+        s_row0[n] = r;
+        s_end[n] = s_starts[g + 1];
+      }
+    s_slots = n;
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_slots = s_slots;
+  const int total_tiles = n_slots * tiles_b;
+  constexpr int B_ROWS = GLU ? BN / 2 : BN;  // features a tile covers
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int it = 0;  // stage uses so far, across tiles
+      bool ok = true;
+      for (int tile = (int)blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int slot = tile % n_slots, tb = tile / n_slots;
+        const int row0 = s_row0[slot];
+        const int b_row = s_group[slot] * p.rows_b + tb * B_ROWS;
+        for (int kb = 0; kb < nkb; ++kb) {
+          const int use = it + kb;
+          const int s = use % STAGES;
+          const uint32_t phase = (uint32_t)(use / STAGES) & 1u;
+          if (use >= STAGES && !mbar_wait(&empty[s], phase ^ 1u, abort_flag, 1, kb)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = tiles + s * Smem<BN>::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + Smem<BN>::A_BYTES;
+          mbar_expect_tx(&full[s], Smem<BN>::STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, &full[s], kb * BK, row0);
+          tma_load_2d(b_dst, &map_b, &full[s], kb * BK, b_row);
+          if constexpr (GLU)
+            tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b, &full[s], kb * BK, b_row + p.rows_b / 2);
+        }
+        it += nkb;
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int tile = (int)blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+        const int buf = j & 1;
+        // the epilogue must have emptied this accumulator (free at its first two uses)
+        if (j >= 2) ok = mbar_wait(&acc_empty[buf], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, 4, j);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < nkb; ++kb) {
+          const int use = it + kb;
+          const int s = use % STAGES;
+          const uint32_t phase = (uint32_t)(use / STAGES) & 1u;
+          ok = mbar_wait(&full[s], phase, abort_flag, 2, kb);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * Smem<BN>::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + Smem<BN>::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma(d_tmem, make_desc(a_addr + k * UMMA_K * 2), make_desc(b_addr + k * UMMA_K * 2),
+                 idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit(&empty[s]);
+        }
+        if (!ok) break;
+        tc_commit(&acc_full[buf]);
+        it += nkb;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    int j = 0;
+    bool ok = true;
+    for (int tile = (int)blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+      const int slot = tile % n_slots, tb = tile / n_slots;
+      const int buf = j & 1;
+      const int row_end = s_end[slot];
+      const long long i_global = (long long)s_row0[slot] + quarter * 32 + lane;
+      ok = mbar_wait(&acc_full[buf], (uint32_t)((j >> 1) & 1), abort_flag, 3, j);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+      if constexpr (GLU) {
+        constexpr int HALF = BN / 2;
+        constexpr int CHUNK = (HALF % 32 == 0) ? 32 : 16;
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + i_global * p.stride_a + (long long)tb * HALF;
+#pragma unroll 1
+        for (int c = 0; c < HALF; c += CHUNK) {
+          uint32_t g[CHUNK], u[CHUNK];
+          if constexpr (CHUNK == 32) {
+            tmem_ld32(lane_addr + (uint32_t)c, g);
+            tmem_ld32(lane_addr + (uint32_t)(HALF + c), u);
+          } else {
+            tmem_ld16(lane_addr + (uint32_t)c, g);
+            tmem_ld16(lane_addr + (uint32_t)(HALF + c), u);
+          }
+          tmem_ld_wait();
+          if (i_global < row_end) {
+#pragma unroll
+            for (int e = 0; e < CHUNK; e += 8) {
+              uint32_t pk[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float r2[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const float gate = fminf(__uint_as_float(g[e + 2 * q + h]), glu.limit);
+                  const float up =
+                      fminf(fmaxf(__uint_as_float(u[e + 2 * q + h]), -glu.limit), glu.limit);
+                  r2[h] = gate * (1.0f / (1.0f + __expf(-glu.alpha * gate))) * (up + glu.shift);
+                }
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(r2[0], r2[1]);
+                pk[q] = *reinterpret_cast<const uint32_t*>(&h2);
+              }
+              *reinterpret_cast<uint4*>(dst + c + e) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
+        }
+      } else {
+        GemmParams mine = p;      // rows of the next group are beyond this tile's bound
+        mine.rows_a = row_end;
+        float* out_f = (float*)p.out;
+        __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
+        constexpr int CHUNK = (BN % 32 == 0) ? 32 : 16;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CHUNK) {
+          float v[CHUNK];
+          if constexpr (CHUNK == 32) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + (uint32_t)c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+          } else {
+            uint32_t r[16];
+            tmem_ld16(lane_addr + (uint32_t)c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
+          }
+          store_chunk<CHUNK>(mine, v, i_global, (long long)tb * BN + c, lane, out_f, out_h);
+        }
+      }
+      // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ persistent
 // The same product for many token rows, as one CTA per SM that walks over
 // tiles (tile index = blockIdx.x, += gridDim.x; the A tile index runs fastest,
@@ -628,6 +853,26 @@ int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParam
 }
 }  // namespace
 
+namespace {
+template <int BN, bool GLU>
+int launch_grouped_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
+                              int slots, int tiles_b, const int* starts, int groups,
+                              const GluRule& glu, cudaStream_t stream) {
+  static bool configured[64] = {};
+  if (fb_first_use_on_device(configured)) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_grouped_persistent_kernel<BN, GLU>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Smem<BN>::BYTES);
+    if (e != cudaSuccess) return fb_fail(2, "gemm_tc_grouped: shared memory opt-in: %s", cudaGetErrorString(e));
+  }
+  const long long bound = (long long)slots * tiles_b;
+  const int ctas = bound < sm_count() ? (int)bound : sm_count();
+  fb_launch(gemm_tc_grouped_persistent_kernel<BN, GLU>, dim3(ctas), dim3(THREADS), Smem<BN>::BYTES,
+            stream, ma, mb, p, starts, groups, glu, tiles_b);
+  return fb_check_launch("gemm_tc_grouped_persistent");
+}
+}  // namespace
+
 // The grouped product (see `gemm_tc_grouped_kernel`): a [rows_a, K] bf16 with rows
 // sorted by group, `starts` [groups + 1] int32 on the device (starts[groups] <=
 // rows_a), b [groups * rows_b, K] bf16 (the groups' matrices stacked);
@@ -635,10 +880,12 @@ int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParam
 // over groups of ceil(rows of the group / 128); rows_a / 128 + groups always is.
 // glu 1: a group's rows are rows_b / 2 gate rows, then as many up rows; out is bf16
 // [rows_a, rows_b / 2] = act(gate) * up with the rule of `gemm_tc_grouped_kernel`.
+// persistent 1: the form with one CTA an SM and two accumulators, where it applies.
 FB_API int fb_gemm_tc_grouped(const void* a, long long lda, int rows_a, const void* b,
                               long long ldb, int rows_b, int K, const int* starts, int groups,
                               int slots, void* out, long long ldo, int out_f32, int glu,
-                              float limit, float alpha, float shift, cudaStream_t stream) {
+                              float limit, float alpha, float shift, int persistent,
+                              cudaStream_t stream) {
   FB_REQUIRE(rows_a > 0 && rows_b > 0 && K > 0 && groups > 0 && slots > 0 && starts != nullptr,
              "gemm_tc_grouped: bad sizes %d x %d x %d in %d groups", rows_a, rows_b, K, groups);
   FB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
@@ -668,6 +915,30 @@ FB_API int fb_gemm_tc_grouped(const void* a, long long lda, int rows_a, const vo
   rc = make_map(&mb, b, (long long)groups * rows_b, K, ldb, glu ? bn / 2 : bn);
   if (rc) return rc;
   const dim3 grid(slots, rows_b / bn);
+  // one CTA an SM over all tiles with two accumulators, where the row tiles fit its table
+  // and there is more than a round of tiles; else a CTA a tile
+  if (persistent && slots <= GROUPED_MAX_SLOTS && groups <= 256 &&
+      (long long)slots * (rows_b / bn) > sm_count()) {
+#define FB_GROUPED_PERSISTENT(BN_, GLU_)                                                       \
+  return launch_grouped_persistent<BN_, GLU_>(ma, mb, p, slots, rows_b / bn, starts, groups, rule, \
+                                              stream)
+    if (glu) {
+      switch (bn) {
+        case 32: FB_GROUPED_PERSISTENT(32, true);
+        case 64: FB_GROUPED_PERSISTENT(64, true);
+        case 128: FB_GROUPED_PERSISTENT(128, true);
+        default: FB_GROUPED_PERSISTENT(256, true);
+      }
+    }
+    switch (bn) {
+      case 16: FB_GROUPED_PERSISTENT(16, false);
+      case 32: FB_GROUPED_PERSISTENT(32, false);
+      case 64: FB_GROUPED_PERSISTENT(64, false);
+      case 128: FB_GROUPED_PERSISTENT(128, false);
+      default: FB_GROUPED_PERSISTENT(256, false);
+    }
+#undef FB_GROUPED_PERSISTENT
+  }
   if (glu) {
     switch (bn) {
       case 32: return launch_grouped<32, true>(ma, mb, p, grid, starts, groups, rule, stream);

@@ -44,7 +44,7 @@ _SIGNATURES = {
                           c_int, c_float, c_void_p],
     "fb_sum_planes": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p],
     "fb_gemm_tc_grouped": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_int,
-                           c_int, c_void_p, c_ll, c_int, c_int, c_float, c_float, c_float,
+                           c_int, c_void_p, c_ll, c_int, c_int, c_float, c_float, c_float, c_int,
                            c_void_p],
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
                    c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int,
@@ -2486,6 +2486,8 @@ MOE_GROUPED_MMA = _os.environ.get("FOUNDRY_B200_MOE_GROUPED_MMA", "1") != "0"
 # Many tokens: every expert's rows through ONE tcgen05 launch a product ("0": a launch
 # per expert through the dense products, which needs the experts' counts on the host)
 MOE_GROUPED_TC = _os.environ.get("FOUNDRY_B200_MOE_GROUPED_TC", "1") != "0"
+# ... as one CTA an SM that walks the tiles with two accumulators ("0": a CTA a tile)
+MOE_GROUPED_TC_PERSISTENT = _os.environ.get("FOUNDRY_B200_MOE_GROUPED_TC_PERSISTENT", "1") != "0"
 
 
 def moe_grouped_tc_fits(x: torch.Tensor, *sizes: int) -> bool:
@@ -2497,8 +2499,8 @@ def moe_grouped_tc_fits(x: torch.Tensor, *sizes: int) -> bool:
 
 
 def gemm_tc_grouped(rows: torch.Tensor, w: torch.Tensor, order: "ExpertOrder",
-                    out_dtype: torch.dtype = torch.float32,
-                    glu: Optional[tuple] = None) -> torch.Tensor:
+                    out_dtype: torch.dtype = torch.float32, glu: Optional[tuple] = None,
+                    persistent: Optional[bool] = None) -> torch.Tensor:
     """out[i] = rows[i] @ w[expert of row i]^T for rows sorted by expert (`order.starts`):
     rows [pairs, K] bfloat16, w [E, N, K] bfloat16 -> [pairs, N], in one launch on the
     tensor cores (csrc/gemm_tcgen05.cu, `gemm_tc_grouped_kernel`). Nothing of the launch
@@ -2523,7 +2525,9 @@ def gemm_tc_grouped(rows: torch.Tensor, w: torch.Tensor, order: "ExpertOrder",
     _call("fb_gemm_tc_grouped", _dev(rows, "rows", contiguous=False), _rows(rows, "rows"), pairs,
           _dev(w, "w"), K, N, K, order.starts.data_ptr(), E, pairs // 128 + E, _dev(out, "out"),
           width, 1 if out_dtype == torch.float32 else 0, 0 if glu is None else 1, float(limit),
-          float(alpha), float(shift), _stream(), tag=("m{} k{} n{}", pairs, K, N))
+          float(alpha), float(shift),
+          1 if (MOE_GROUPED_TC_PERSISTENT if persistent is None else persistent) else 0, _stream(),
+          tag=("m{} k{} n{}", pairs, K, N))
     return out
 
 

@@ -1106,19 +1106,22 @@ def _many_rows_norm(ops, M, H, K):
 
 @pytest.mark.parametrize("sizes", [(64, 48, [0, 1, 128, 129, 300, 0, 7]), (200, 256, [130, 0, 0, 5]),
                                    (512, 160, [1000, 24]), (72, 16, [3]), (128, 512, [5, 260, 0, 1]),
-                                   (96, 96, [129, 127]), (64, 64, [40])])
-def test_gemm_tc_grouped(sizes):
-    """The grouped tcgen05 product: groups of no rows, one row, exactly a tile and a tile
-    and a row; K that is no multiple of a K block; tile widths 16 to 256; float32 and
-    bfloat16 outputs. Rows of the next group that a tile reads are not stored."""
+                                   (96, 96, [129, 127]), (64, 64, [40]),
+                                   (64, 2048, [700, 0, 3000, 129, 1]), (256, 512, [2500] * 9)])
+@pytest.mark.parametrize("persistent", [False, True])
+def test_gemm_tc_grouped(sizes, persistent):
+    """The grouped tcgen05 product, a CTA a tile and one CTA an SM over all tiles (the
+    last two sizes have more tiles than SMs): groups of no rows, one row, exactly a tile and
+    a tile and a row; K that is no multiple of a K block; tile widths 16 to 256; float32
+    and bfloat16 outputs. Rows of the next group that a tile reads are not stored."""
     from foundry_b200.kernels import ops
     K, N, counts = sizes
     E, pairs = len(counts), sum(counts)
     gen = torch.Generator().manual_seed(K + N)
     rows = torch.randn(pairs, K, generator=gen).to(torch.bfloat16)
     w = (torch.randn(E, N, K, generator=gen) / K ** 0.5).to(torch.bfloat16)
-    group = torch.repeat_interleave(torch.arange(E), torch.tensor(counts))
-    want = torch.einsum("ik,ink->in", rows.float(), w.float()[group])
+    edges = [0] + list(np.cumsum(counts))
+    want = torch.cat([rows[edges[e]:edges[e + 1]].float() @ w[e].float().T for e in range(E)])
 
     class Order:  # what the sort of the pairs leaves, made by hand
         experts, starts = E, torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32,
@@ -1126,7 +1129,7 @@ def test_gemm_tc_grouped(sizes):
     Order.pairs = pairs
     for out_dtype, tol in ((torch.float32, 2e-3), (torch.bfloat16, 2e-2)):
         guard = torch.full((pairs + 256, N), 7.0, dtype=out_dtype, device="cuda")
-        got = ops.gemm_tc_grouped(rows.cuda(), w.cuda(), Order, out_dtype)
+        got = ops.gemm_tc_grouped(rows.cuda(), w.cuda(), Order, out_dtype, persistent=persistent)
         torch.cuda.synchronize()
         ops.raise_on_device_failure()
         assert torch.allclose(got.float().cpu(), want, rtol=tol, atol=tol), (sizes, out_dtype)
@@ -1137,7 +1140,8 @@ def test_gemm_tc_grouped(sizes):
             g, u = want[:, :N // 2], want[:, N // 2:]
             gc, uc = g.clamp(max=limit), u.clamp(-limit, limit)
             act = gc * torch.sigmoid(alpha * gc) * (uc + shift)
-            got = ops.gemm_tc_grouped(rows.cuda(), w.cuda(), Order, glu=(limit, alpha, shift))
+            got = ops.gemm_tc_grouped(rows.cuda(), w.cuda(), Order, glu=(limit, alpha, shift),
+                                      persistent=persistent)
             torch.cuda.synchronize()
             ops.raise_on_device_failure()
             assert got.dtype == torch.bfloat16 and tuple(got.shape) == (pairs, N // 2)
